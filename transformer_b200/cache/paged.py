@@ -130,7 +130,8 @@ class Cache:
                  reads_from: Sequence[Optional[int]], *, max_tokens: int, max_context: int,
                  max_slots: Optional[int], dtype: torch.dtype, device: torch.device,
                  named_states: Optional[Dict[str, StateNeed]] = None):
-        """cache_needs[r] / state_needs[r]: what run r's mixer asks for; reads_from[r]: the run whose
+        """cache_needs[r] / state_needs[r]: what run r's mixer asks for (state_needs[r] may be a dict, part name ->
+        StateNeed, for a block in which several parts carry state); reads_from[r]: the run whose
         cache run r reads instead of owning one; named_states: per-sequence state of parts that are not a run's
         mixer (the embedding), by name."""
         if max_tokens <= 0:
@@ -165,9 +166,13 @@ class Cache:
                     raise CacheError(f"run {r} reads the cache of run {src}, which owns none")
                 if cache_needs[src] != cache_needs[r]:
                     raise CacheError(f"run {r} reads the cache of run {src}, but they need different storage")
-        self.state: Dict[int, torch.Tensor] = {}
+        self.state: Dict[int, object] = {}    # run -> tensor, or {part name: tensor} for a block with several
         for r, need in enumerate(state_needs):
-            if need is not None:
+            if isinstance(need, dict):
+                if need:
+                    self.state[r] = {n: torch.zeros((max_slots, *v.shape), dtype=v.dtype, device=device)
+                                     for n, v in need.items()}
+            elif need is not None:
                 self.state[r] = torch.zeros((max_slots, *need.shape), dtype=need.dtype, device=device)
         self.named: Dict[str, torch.Tensor] = {}
         for name, need in (named_states or {}).items():
@@ -176,13 +181,20 @@ class Cache:
     # ---- sequences ------------------------------------------------------------------------
     def open(self) -> int:
         slot = self.table.open()
-        for t in self.state.values():
+        for t in self._state_tensors():
             t[slot].zero_()
         for t in self.named.values():
             t[slot].zero_()
         for g in self.groups:
             g.open(slot)
         return slot
+
+    def _state_tensors(self):
+        for t in self.state.values():
+            if isinstance(t, dict):
+                yield from t.values()
+            else:
+                yield t
 
     def close(self, slot: int) -> None:
         self.table.close(slot)
@@ -210,10 +222,11 @@ class Cache:
         g, i = self._where[owner]
         return self.groups[g].view(i, src is None)
 
-    def state_of(self, run: int) -> Optional[torch.Tensor]:
+    def state_of(self, run: int):
+        """The run's state tensor [slots, ...], or a dict of them by part name, or None."""
         return self.state.get(run)
 
     @property
     def nbytes(self) -> int:
-        return sum(g.nbytes for g in self.groups) + sum(t.numel() * t.element_size() for t in self.state.values()) + \
+        return sum(g.nbytes for g in self.groups) + sum(t.numel() * t.element_size() for t in self._state_tensors()) + \
             sum(t.numel() * t.element_size() for t in self.named.values())

@@ -2,8 +2,12 @@
 // heads of different sizes and a gate on the output: the general kernel (CUDA cores, float or bfloat16).
 //
 //   score(q at position p, key at position j) = cap(q . k * scale),   cap(s) = softcap * tanh(s / softcap)  (softcap > 0)
-//   visible iff j <= p and (p - j < window or j < keep_first)
+//   visible iff j <= p and (p - j < window or j < keep_first) and (chunk == 0 or j / chunk == p / chunk)
 //   out[t, h, :] = softmax over the visible keys . v  * sigmoid(gate[t, h, :])                (gate may be absent)
+//   sink (may be absent): a number per head that joins the softmax's denominator as exp(sink_h), with no key and no
+//       value, neither scaled nor capped
+//   values cached rotated (may be absent): the head's output at position p is turned back before the gate, pair
+//       (2m, 2m + 1) by -p * g_m, from the tables ocos / osin [positions, dv / 2]
 //
 // All arithmetic is float (scores, the cap, running maximum, sum, output accumulator).  Keys [pages, nkvh, 64, dk] and
 // values [pages, nkvh, 64, dv] of the step's own tokens are already in the cache.  The cache keeps every position:
@@ -34,6 +38,10 @@ struct WinArgs {
     const int* tok_pos;
     const int* page_table;
     float* partial;         // [nt, nh, splits, dv + 2] when splits > 1
+    const float* sinks;     // [nh] or null
+    const float* ocos;      // [positions, dv / 2] or null
+    const float* osin;
+    int chunk;              // 0: none
     int max_pages, q_stride, gate_stride, nh, nkvh, dk, dv, hc, splits, window, keep_first;
     float scale, softcap;
 };
@@ -68,7 +76,8 @@ __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(const W
     const int pos_first = a.tok_pos[t0];
     const int pos_last = pos_first + nq - 1;
     // the tiles to visit: those of the kept first tokens that lie before the window's, then the window's
-    const int win_lo = a.window > pos_first ? 0 : pos_first - a.window + 1;
+    int win_lo = a.window > pos_first ? 0 : pos_first - a.window + 1;
+    if (a.chunk > 0) win_lo = max(win_lo, pos_first / a.chunk * a.chunk);     // nothing before the first row's chunk
     const int win_t0 = win_lo / AW_KEYS, win_t1 = pos_last / AW_KEYS + 1;
     const int kept = min(a.keep_first, pos_last + 1);
     const int first = min((kept + AW_KEYS - 1) / AW_KEYS, win_t0);
@@ -115,7 +124,8 @@ __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(const W
             s *= a.scale;
             if (a.softcap > 0.f) s = a.softcap * tanhf(s * inv_cap);
             const int j = key0 + lane;
-            const bool see = j <= pos_r && (pos_r - j < a.window || j < a.keep_first);
+            const bool see = j <= pos_r && (pos_r - j < a.window || j < a.keep_first) &&
+                             (a.chunk <= 0 || j / a.chunk == pos_r / a.chunk);
             s = see ? s : -INFINITY;
             const float m_new = fmaxf(m[i], warp_max(s));
             if (m_new == -INFINITY) continue;
@@ -145,12 +155,31 @@ __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(const W
         if (a.splits == 1) {
             T* dst = static_cast<T*>(a.out) + ((size_t)t * a.nh + h) * dv;
             const T* gt = a.gate ? static_cast<const T*>(a.gate) + (size_t)t * a.gate_stride + (size_t)h * dv : nullptr;
-            const float inv = 1.0f / l[i];
+            float lsum = l[i], keep = 1.f;
+            if (a.sinks) {          // the sink joins the denominator; the larger of it and the maximum stays the reference
+                const float sk = a.sinks[h];
+                if (sk > m[i]) {
+                    keep = expf(m[i] - sk);
+                    lsum = lsum * keep + 1.f;
+                } else {
+                    lsum += expf(sk - m[i]);
+                }
+            }
+            const float inv = keep / lsum;
+            const int pos_t = a.ocos ? a.tok_pos[t] : 0;
 #pragma unroll
             for (int c = 0; c < DPL; ++c) {
                 const int ch = lane + 32 * c;
+                float v = o[i][c] * inv;
+                if (a.ocos) {       // the pair's other entry sits in the neighbouring lane
+                    const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+                    if (ch < dv) {
+                        const float co = a.ocos[(size_t)pos_t * (dv / 2) + (ch >> 1)];
+                        const float si = a.osin[(size_t)pos_t * (dv / 2) + (ch >> 1)];
+                        v = (ch & 1) ? v * co - other * si : v * co + other * si;
+                    }
+                }
                 if (ch < dv) {
-                    float v = o[i][c] * inv;
                     if (gt) v *= 1.0f / (1.0f + expf(-ldf(gt + ch)));
                     stf(dst + ch, v);
                 }
@@ -173,13 +202,15 @@ __global__ void __launch_bounds__(AW_WARPS * 32) attention_window_kernel(const W
 // out[t, h, :] = sum_s o_s exp(m_s - m) / sum_s l_s exp(m_s - m) * sigmoid(gate),  m = max_s m_s.
 template <typename T>
 __global__ void attention_window_merge_kernel(const float* __restrict__ partial, T* __restrict__ out,
-                                              const T* __restrict__ gate, int gate_stride, int nh, int dv, int splits) {
+                                              const T* __restrict__ gate, int gate_stride, int nh, int dv, int splits,
+                                              const float* __restrict__ sinks, const float* __restrict__ ocos,
+                                              const float* __restrict__ osin, const int* __restrict__ tok_pos) {
     pdl_sync();
     const int t = blockIdx.x, h = blockIdx.y;
     const float* p = partial + ((size_t)t * nh + h) * splits * (dv + 2);
-    float m = -INFINITY;
+    float m = sinks ? sinks[h] : -INFINITY;
     for (int s = 0; s < splits; ++s) m = fmaxf(m, p[s * (dv + 2) + dv]);
-    float den = 0.f;
+    float den = sinks ? expf(sinks[h] - m) : 0.f;
     for (int s = 0; s < splits; ++s) {
         const float ms = p[s * (dv + 2) + dv];
         if (ms != -INFINITY) den += p[s * (dv + 2) + dv + 1] * expf(ms - m);
@@ -191,6 +222,16 @@ __global__ void attention_window_merge_kernel(const float* __restrict__ partial,
             if (ms != -INFINITY) acc += p[s * (dv + 2) + c] * expf(ms - m);
         }
         float v = acc / den;
+        if (ocos) {             // turn the pair (c, c ^ 1) back: the other entry is summed here as well
+            float other = 0.f;
+            for (int s = 0; s < splits; ++s) {
+                const float ms = p[s * (dv + 2) + dv];
+                if (ms != -INFINITY) other += p[s * (dv + 2) + (c ^ 1)] * expf(ms - m);
+            }
+            other /= den;
+            const float co = ocos[(size_t)tok_pos[t] * (dv / 2) + (c >> 1)], si = osin[(size_t)tok_pos[t] * (dv / 2) + (c >> 1)];
+            v = (c & 1) ? v * co - other * si : v * co + other * si;
+        }
         if (gate) v *= 1.0f / (1.0f + expf(-ldf(gate + (size_t)t * gate_stride + (size_t)h * dv + c)));
         stf(out + ((size_t)t * nh + h) * dv + c, v);
     }
@@ -219,6 +260,7 @@ static int window_launch(WinArgs a, int tiles, int nt, cudaStream_t s) {
     if (a.nh <= 0 || a.nkvh <= 0 || a.nh % a.nkvh || a.window <= 0 || a.keep_first < 0) return TB_ERR_ARG;
     if (a.dk <= 0 || a.dv <= 0 || a.dk > 256 || a.dv > 256) return TB_ERR_UNSUPPORTED;
     if (a.splits < 1 || (a.splits > 1 && !a.partial)) return TB_ERR_ARG;
+    if (a.chunk < 0 || (a.ocos && (!a.osin || a.dv % 2))) return TB_ERR_ARG;
     if (tiles <= 0 || nt <= 0) return tiles == 0 || nt == 0 ? 0 : TB_ERR_ARG;
     const int group = a.nh / a.nkvh;
     a.hc = group < AW_ROWS ? group : AW_ROWS;
@@ -237,7 +279,7 @@ static int window_launch(WinArgs a, int tiles, int nt, cudaStream_t s) {
     if (a.splits > 1) {
         dim3 grid(nt, a.nh);
         TB_LAUNCH((attention_window_merge_kernel<T>), grid, a.dv < 128 ? 64 : 128, 0, s, a.partial, (T*)a.out,
-                  (const T*)a.gate, a.gate_stride, a.nh, a.dv, a.splits);
+                  (const T*)a.gate, a.gate_stride, a.nh, a.dv, a.splits, a.sinks, a.ocos, a.osin, a.tok_pos);
         rc = tb_last_error();
     }
     return rc;
@@ -248,9 +290,11 @@ extern "C" {
     int NAME(const void* q, void* out, const void* kc, const void* vc, const void* gate, const int* tile_seq,         \
              const int* tile_t0, const int* tile_nq, const int* tok_pos, const int* page_table, float* partial,       \
              int tiles, int nt, int max_pages, int q_stride, int gate_stride, int nh, int nkvh, int dk, int dv,       \
-             int splits, int window, int keep_first, float scale, float softcap, cudaStream_t s) {                    \
-        WinArgs a{q, out, kc, vc, gate, tile_seq, tile_t0, tile_nq, tok_pos, page_table, partial, max_pages,          \
-                  q_stride, gate_stride, nh, nkvh, dk, dv, 0, splits, window, keep_first, scale, softcap};            \
+             int splits, int window, int keep_first, float scale, float softcap, int chunk, const float* sinks,       \
+             const float* ocos, const float* osin, cudaStream_t s) {                                                  \
+        WinArgs a{q, out, kc, vc, gate, tile_seq, tile_t0, tile_nq, tok_pos, page_table, partial, sinks, ocos, osin,  \
+                  chunk, max_pages, q_stride, gate_stride, nh, nkvh, dk, dv, 0, splits, window, keep_first, scale,    \
+                  softcap};                                                                                           \
         return window_launch<T>(a, tiles, nt, s);                                                                     \
     }
 TB_ATTENTION_WINDOW(tb_attention_window_f32, float)

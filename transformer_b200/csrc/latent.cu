@@ -17,7 +17,7 @@
 
 // ---- preparation -----------------------------------------------------------------------------------
 // One block per token.  a[t] = [ zq: q_rank | zc: rank | zr: rot ] (the last two only for a layer that owns a
-// latent).  cq[t] = zq / rms(zq) * wq;  cache row of (sequence, position) = [ zc / rms(zc) * wc | rotate(zr) ].
+// latent; q_rank may be 0 for a mixer whose queries come straight from a projection).  cq[t] = zq / rms(zq) * wq;  cache row of (sequence, position) = [ zc / rms(zc) * wc | rotate(zr) ].
 // rotate: entries i and i + rdims/2 (i < rdims/2) are a pair, angle = position * base^(-2i/rdims) from the
 // tables cos/sin [positions, rdims/2]; entries from rdims on pass.
 template <typename T>
@@ -270,7 +270,7 @@ int tb_latent_attention_tile_tokens(int H) {
                              void* cache, const int* tok_seq, const int* tok_pos, const int* page_table,              \
                              int max_pages, const float* cosT, const float* sinT, int nt, int q_rank, int rank,       \
                              int rot, int rdims, cudaStream_t s) {                                                    \
-        if (nt < 0 || q_rank <= 0 || rank <= 0 || rot < 0 || rdims < 0 || rdims > rot || rdims % 2) return TB_ERR_ARG; \
+        if (nt < 0 || q_rank < 0 || (q_rank && (!wq || !cq)) || rank <= 0 || rot < 0 || rdims < 0 || rdims > rot || rdims % 2) return TB_ERR_ARG; \
         if (cache && (!wc || !tok_seq || !tok_pos || !page_table || (rdims && (!cosT || !sinT)))) return TB_ERR_ARG;  \
         if (nt == 0) return 0;                                                                                        \
         TB_LAUNCH((latent_prep_kernel<T>), nt, 128, 0, s, (const T*)a, lda, wq, wc, eps, (T*)cq, (T*)cache, tok_seq,  \

@@ -63,7 +63,11 @@ _SIGNATURES: Dict[str, str] = {
     "tb_embed_bigram_f32": "pppppppppiifiii", "tb_embed_bigram_bf16": "pppppppppiifiii",
     "tb_scale_f32": "plf",
     "tb_qknorm_rope_cache_f32": "pippfpppippppiiiiiii", "tb_qknorm_rope_cache_bf16": "pippfpppippppiiiiiii",
-    "tb_attention_window_f32": "pppppppppppiiiiiiiiiiiiff", "tb_attention_window_bf16": "pppppppppppiiiiiiiiiiiiff",
+    "tb_attention_window_f32": "pppppppppppiiiiiiiiiiiiffippp", "tb_attention_window_bf16": "pppppppppppiiiiiiiiiiiiffippp",
+    "tb_pair_add_rmsnorm_f32": "ppppppippifii", "tb_pair_add_rmsnorm_bf16": "ppppppippifii",
+    "tb_conv_roll_f32": "piplppiii", "tb_conv_roll_bf16": "piplppiii",
+    "tb_causal_conv_f32": "pipplpipppiiiiii", "tb_causal_conv_bf16": "pipplpipppiiiiii",
+    "tb_head_prep_f32": "pipplpppfppppppppppppiiiiiiiii", "tb_head_prep_bf16": "pipplpppfppppppppppppiiiiiiiii",
     "tb_attention_window_mma_bf16": "pppppppppppiiiiiiiiiiiiff",
     "tb_delta_prep_f32": "pipppppppppppiiiiiiii",
     "tb_delta_prep_bf16": "pipppppppppppiiiiiiii",
@@ -75,7 +79,7 @@ class TapeArg(ctypes.Union):
                 ("u", ctypes.c_ulonglong)]
 
 
-TAPE_MAX_ARGS = 28
+TAPE_MAX_ARGS = 32
 
 
 class TapeEntry(ctypes.Structure):

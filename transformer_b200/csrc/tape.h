@@ -16,7 +16,7 @@
 #include <tuple>
 #include <utility>
 
-#define TB_TAPE_MAX_ARGS 28
+#define TB_TAPE_MAX_ARGS 32
 
 union TapeArg {
     const void* p;

@@ -21,7 +21,7 @@ from ..cache.paged import Cache
 from ..cache.slots import CacheError
 from ..csrc import lib
 from ..parts.block import build_layer, resolve
-from ..parts.base import EMBEDDINGS, HEADS, NORMS, NormedDelta
+from ..parts.base import EMBEDDINGS, HEADS, JOINTS, NORMS, NormedDelta, PairDelta
 from ..parts.spec import ModelSpec
 from .context import StepContext, Workspace, weak_callback
 from .tape import LayerTape, moves, run_tensors
@@ -38,6 +38,8 @@ def _pending_signature(pending):
         return None
     if isinstance(pending, torch.Tensor):
         return ("t", pending.data_ptr(), tuple(pending.shape))
+    if isinstance(pending, PairDelta):
+        return ("p", _pending_signature(pending.first), _pending_signature(pending.second))
     if isinstance(pending, NormedDelta):      # names a weight of the layer before: equal only for the same layer
         return ("n", _pending_signature(pending.delta), pending.weight.data_ptr(), pending.eps)
     return ("w", pending.rows.data_ptr(), pending.index.data_ptr(), pending.weights.data_ptr(), pending.k,
@@ -61,10 +63,14 @@ class Engine:
         self.layers = [build_layer(ls, dtype, device) for ls in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm, dtype, device)
         self.head_part = HEADS.build(spec.head, dtype, device)
+        self.joints = [JOINTS.build(j, dtype, device) for j in spec.joints]
         self._bind(weights)
         runs = spec.order
         mixers = [self.layers[e.layer].mixer for e in runs]
-        self.cache = Cache([m.cache_need() for m in mixers], [m.state_need() for m in mixers],
+        # a block in which parts other than the mixer carry state says so itself (name -> need)
+        state_needs = [self.layers[e.layer].state_needs() if hasattr(self.layers[e.layer], "state_needs")
+                       else self.layers[e.layer].mixer.state_need() for e in runs]
+        self.cache = Cache([m.cache_need() for m in mixers], state_needs,
                            [e.cache_of for e in runs], max_tokens=max_tokens, max_context=spec.max_context,
                            max_slots=max_slots, dtype=dtype, device=device,
                            named_states={"embedding": self.embed.state_need()} if self.embed.state_need() else None)
@@ -81,7 +87,8 @@ class Engine:
         # decode steps (one token per sequence) replay a CUDA graph captured per batch size, if every part of the
         # model says that its forward is fit for that (Part.graph_safe); one part that runs Python per step
         # (reads host lists, branches on values) keeps the whole model on eager steps
-        self.graph_safe = all(p.graph_safe for p in [self.embed, self.final_norm, self.head_part, *self.layers])
+        self.graph_safe = all(p.graph_safe for p in [self.embed, self.final_norm, self.head_part, *self.layers,
+                                                     *self.joints])
         self.use_graphs = True
         self.graph_max_batch = 256
         # layers of equal parts are recorded once per step and replayed from C++ for the other runs (engine/tape.py)
@@ -106,6 +113,8 @@ class Engine:
             for pname, part in layer.parts().items():
                 part.bind({n: weights[("layers", i, pname, n)] for n in part.parameters()})
         self.final_norm.bind({n: weights[("final_norm", n)] for n in self.final_norm.parameters()})
+        for i, joint in enumerate(self.joints):
+            joint.bind({n: weights[("joints", i, n)] for n in joint.parameters()})
 
     @property
     def embedding(self) -> torch.Tensor:
@@ -340,12 +349,16 @@ class Engine:
             self.embed.forward(ctx, x, state=self._embed_state)     # an embedding that carries something per sequence
         else:
             self.embed.forward(ctx, x)
+        for joint in self.joints:
+            joint.begin(ctx, x)       # what a joint keeps of the embedding output
         pending = None
         taping = self.use_tapes and self.recorder is None
         tapes = {}                  # kind of run and of what it is handed -> (recorded run, its tape)
         for r, entry in enumerate(self.spec.order):
             layer = self.layers[entry.layer]
             ctx.run_index = r
+            if entry.joint is not None:
+                pending = self.joints[entry.joint].forward(ctx, x, pending)
             kind = self._run_kind[r] if taping else None
             if kind is None:
                 pending = layer.forward(ctx, x, pending, self.cache.view(r), self.cache.state_of(r))

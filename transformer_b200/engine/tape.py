@@ -85,7 +85,9 @@ def run_tensors(layer, cache_view, state) -> Optional[List[torch.Tensor]]:
         if not held or not all(isinstance(t, torch.Tensor) for t in held):
             return None
         out += list(held)
-    if state is not None:
+    if isinstance(state, dict):
+        out += [state[n] for n in sorted(state)]
+    elif state is not None:
         out.append(state)
     return out
 

@@ -13,6 +13,16 @@ the WHOLE query projection and the whole key projection before the rotation (``q
 below the head's); a gate on the output, o * sigmoid(Wg x1), whose projection rides in the merged product
 (``gate``).  With any of them the step runs  merged product -> norm + rotation + cache write (one kernel) ->
 windowed attention with the gate in its epilogue -> output product  (csrc/attention_window.cu, rope_cache.cu).
+
+A second family, again parameters of the same mixer: a short causal convolution over time on every channel of the
+q, k and v projections, ``conv_taps`` wide (weights ``conv``; the last ``conv_taps - 1`` projected rows are state of
+the sequence); an RMS norm per head with one weight of the head's size shared by all heads (``qk_norm="head"``); a
+learned multiplier of every query head's scores (``temperature``, weights ``temp``); values that are cached rotated
+by their own position over all of their entries, in adjacent pairs, with the rotary part's base and no rescaling,
+and an output that is turned back by the query's position (``value_rotation``); a mask of chunks (``chunk``:
+position i sees j <= i iff i // chunk == j // chunk); a learned number per head that joins the softmax's
+denominator (``sink``, weights ``sink``).  With any of these the kernel between the product and the attention is
+``tb_head_prep`` (csrc/head_prep.cu): convolution, norms, temperature, both rotations and the cache write at once.
 """
 from __future__ import annotations
 
@@ -21,7 +31,7 @@ import math
 import torch
 
 from ..csrc import lib
-from .base import MIXERS, POSITIONS, CacheNeed, Mixer, ParamDecl
+from .base import MIXERS, POSITIONS, CacheNeed, Mixer, ParamDecl, StateNeed
 from .linear import matmul_nt
 from .spec import PartSpec
 
@@ -57,13 +67,24 @@ class Attention(Mixer):
         self.qk_norm = params.get("qk_norm")
         self.gate = bool(params.get("gate", False))
         self.eps = float(params.get("eps", 0.0))
-        if self.qk_norm not in (None, "whole"):
+        if self.qk_norm not in (None, "whole", "head"):
             raise ValueError(f"unknown query/key norm {self.qk_norm!r}")
+        self.conv_taps = int(params.get("conv_taps") or 0)          # 0: no convolution on the projections
+        self.temperature = bool(params.get("temperature", False))
+        self.value_rotation = bool(params.get("value_rotation", False))
+        self.chunk = int(params.get("chunk") or 0)
+        self.sink = bool(params.get("sink", False))
+        if self.conv_taps < 0 or self.conv_taps > 16 or self.chunk < 0:
+            raise ValueError("convolutions of 1 to 16 taps; chunk not negative")
+        # the second family of mechanisms: its own kernel between the product and the attention
+        self.prepared = bool(self.conv_taps or self.qk_norm == "head" or self.temperature or self.value_rotation)
+        if self.prepared and (self.gate or self.qk_norm == "whole"):
+            raise ValueError("a norm over the whole projection or an output gate does not go with the per-head family")
         if self.dv <= 0 or self.dv > 256 or self.window < 0 or self.keep_first < 0 or self.softcap < 0:
             raise ValueError("value heads of 1..256 entries; window, keep_first and softcap not negative")
         # any of the further mechanisms takes the step to the windowed kernels
         self.extended = bool(self.dv != self.dh or self.softcap or self.window or self.qk_norm or self.gate or
-                             "scale" in params)
+                             "scale" in params or self.prepared or self.chunk or self.sink)
         if not self.extended and (self.dh % 16):
             raise ValueError(f"the attention kernels take head sizes 16, 32, ..., 256; got {self.dh}")
         self.rdims = 0
@@ -73,6 +94,13 @@ class Attention(Mixer):
             self.rdims = int(pos.get()["dh"])
             if self.rdims > self.dh:
                 raise ValueError(f"a rotation of {self.rdims} entries does not fit heads of {self.dh}")
+        self.value_position = None
+        if self.value_rotation:
+            if self.dv % 2 or not isinstance(pos, PartSpec):
+                raise ValueError("rotated values need an even value size and the rotary part whose base they share")
+            pp = pos.get()
+            self.value_position = POSITIONS.build(PartSpec.of("rope", dh=self.dv, theta=pp["theta"], pairing="adjacent",
+                                                              positions=pp["positions"]), dtype, device)
         self.qkv_width = (self.nh + self.nkvh) * self.dh + self.nkvh * self.dv + (self.nh * self.dv if self.gate else 0)
         self.scale = float(params["scale"]) if "scale" in params else 1.0 / math.sqrt(self.dh)
         # query tiles this mixer asks the step to plan: the general kernel's, and the prompt kernel's
@@ -100,9 +128,18 @@ class Attention(Mixer):
             "wqkv": ParamDecl((self.qkv_width, self.d)),
             "wo": ParamDecl((self.d, self.nh * self.dv)),
         }
-        if self.qk_norm:
+        if self.qk_norm == "whole":
             decl["q_norm"] = ParamDecl((self.nh * self.dh,), "norm", "ones")
             decl["k_norm"] = ParamDecl((self.nkvh * self.dh,), "norm", "ones")
+        elif self.qk_norm == "head":
+            decl["q_norm"] = ParamDecl((self.dh,), "norm", "ones")
+            decl["k_norm"] = ParamDecl((self.dh,), "norm", "ones")
+        if self.conv_taps:
+            decl["conv"] = ParamDecl((self.qkv_width, self.conv_taps), "norm", "normal")
+        if self.temperature:
+            decl["temp"] = ParamDecl((self.nh,), "norm", "ones")
+        if self.sink:
+            decl["sink"] = ParamDecl((self.nh,), "norm", "normal")
         if self.position is not None:      # what the position encoding has learned travels with its mixer
             decl.update({"position." + n: d for n, d in self.position.parameters().items()})
         return decl
@@ -116,6 +153,44 @@ class Attention(Mixer):
         if self.dv != self.dh:
             return CacheNeed("full", self.nkvh, self.dh, (("dv", self.dv),))
         return CacheNeed("full", self.nkvh, self.dh)
+
+    def state_need(self):
+        if self.conv_taps > 1:      # the convolutions' last inputs: the projected rows before the step's first
+            return StateNeed(((self.conv_taps - 1) * self.qkv_width,), torch.float32)
+        return None
+
+    def _forward_prepared(self, ctx, x1, out, cache, state) -> None:
+        """The step of the per-head family: see the head of this file."""
+        nt = x1.shape[0]
+        sfx = lib.suffix(self.dtype)
+        w = self.weights
+        z = ctx.scratch("attn.qkv", (nt, self.qkv_width), self.dtype)        # q | k | v as the product leaves them
+        matmul_nt(x1, w["wqkv"], z)
+        table = ctx.page_table(cache)
+        cos = sin = vcos = vsin = None
+        if self.rdims:
+            cos, sin, half = self.position.rotation()
+            if half:
+                raise ValueError("the per-head family rotates adjacent pairs")
+        if self.value_position is not None:
+            vcos, vsin, _ = self.value_position.rotation()
+        kc, vc = (cache.k, cache.v) if cache.writable else (None, None)
+        q = ctx.scratch("attn.q", (nt, self.nh * self.dh), self.dtype)
+        lib.call("tb_head_prep_" + sfx, lib.ptr(z), self.qkv_width, lib.ptr(w.get("conv")), lib.ptr(state),
+                 0 if state is None else state.stride(0), lib.ptr(w.get("q_norm")), lib.ptr(w.get("k_norm")),
+                 lib.ptr(w.get("temp")), self.eps, lib.ptr(cos), lib.ptr(sin), lib.ptr(vcos), lib.ptr(vsin), lib.ptr(q),
+                 lib.ptr(kc), lib.ptr(vc), lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(ctx.seq_start),
+                 lib.ptr(ctx.slots), lib.ptr(table), ctx.max_pages, nt, self.nh, self.nkvh, self.dh, self.dv,
+                 self.rdims, max(self.conv_taps, 1), 1 if ctx.decode else 0)
+        if self.conv_taps > 1 and not ctx.decode:
+            # every token has read the old inputs: the state moves on to the step's last rows
+            lib.call("tb_conv_roll_" + sfx, lib.ptr(z), self.qkv_width, lib.ptr(state), state.stride(0),
+                     lib.ptr(ctx.seq_start), lib.ptr(ctx.slots), ctx.B, self.qkv_width, self.conv_taps)
+        o = ctx.scratch("attn.o", (nt, self.nh * self.dv), self.dtype)
+        window = self.window if self.window else 1 << 30
+        run_window_attention(ctx, self, q, o, None, cache, table, nt, window, q_stride=self.nh * self.dh,
+                             sinks=w.get("sink"), ocos=vcos, osin=vsin)
+        matmul_nt(o, w["wo"], out)
 
     def _forward_window(self, ctx, x1, out, cache) -> None:
         """The step with the further mechanisms: see the head of this file."""
@@ -137,10 +212,14 @@ class Attention(Mixer):
         o = ctx.scratch("attn.o", (nt, self.nh * self.dv), self.dtype)
         gate = z[:, (self.nh + self.nkvh) * self.dh + self.nkvh * self.dv:] if self.gate else None
         window = self.window if self.window else 1 << 30
-        run_window_attention(ctx, self, z, o, gate, cache, table, nt, window)
+        run_window_attention(ctx, self, z, o, gate, cache, table, nt, window,
+                             sinks=w.get("sink") if self.sink else None)
         matmul_nt(o, w["wo"], out)
 
     def forward(self, ctx, x1, out, cache, state) -> None:
+        if self.prepared:
+            self._forward_prepared(ctx, x1, out, cache, state)
+            return
         if self.extended:
             self._forward_window(ctx, x1, out, cache)
             return
@@ -245,10 +324,14 @@ class Attention(Mixer):
                             ctx.max_pages, self.qkv_width, self.nh, self.nkvh, self.dh, splits, self.scale)
 
 
-def run_window_attention(ctx, m, z, o, gate, cache, table, nt, window) -> None:
-    """The windowed attention of the step's rotated queries ``z`` over the cache, into ``o`` (gate applied)."""
+def run_window_attention(ctx, m, z, o, gate, cache, table, nt, window, q_stride=None, sinks=None, ocos=None,
+                         osin=None) -> None:
+    """The windowed attention of the step's rotated queries ``z`` over the cache, into ``o`` (gate applied).
+    ``sinks``: a number per head in the softmax's denominator; ``ocos, osin``: tables that turn the output back."""
     sfx = lib.suffix(m.dtype)
-    if m.window_tile and USE_WINDOW_MMA:
+    q_stride = m.qkv_width if q_stride is None else q_stride
+    plain = sinks is None and ocos is None and not m.chunk
+    if m.window_tile and USE_WINDOW_MMA and plain:
         # bfloat16: the tensor-core kernel, for prompts and decoding alike.  Slices of the visited pages so that a few
         # sequences still fill the GPU: a function of the batch's shape alone (a captured graph keeps it)
         tiles = ctx.tiles(m.window_tile)
@@ -257,16 +340,17 @@ def run_window_attention(ctx, m, z, o, gate, cache, table, nt, window) -> None:
         partial = ctx.scratch("attn.partial", (nt, m.nh, splits, m.dv + 2), torch.float32) if splits > 1 else None
         if lib.try_call("tb_attention_window_mma_bf16", lib.ptr(z), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
                         lib.ptr(gate), lib.ptr(tiles.seq), lib.ptr(tiles.t0), lib.ptr(tiles.nq), lib.ptr(ctx.tok_pos),
-                        lib.ptr(table), lib.ptr(partial), tiles.count, nt, ctx.max_pages, m.qkv_width, m.qkv_width,
+                        lib.ptr(table), lib.ptr(partial), tiles.count, nt, ctx.max_pages, q_stride, m.qkv_width,
                         m.nh, m.nkvh, m.dh, m.dv, splits, window, m.keep_first, m.scale, m.softcap):
             return
     tiles = ctx.tiles(m.general_tile)
     # slices of the visited keys so that a few sequences still fill the GPU: a function of the batch's shape alone (a
     # captured graph keeps it), and no more than the window has 32-key tiles
     splits = ctx.attention_splits(tiles.count, m.nh, m.nkvh)
-    splits = int(max(1, min(splits, (min(window, 1 << 20) + m.keep_first + 31) // 32 + 1)))
+    reach = min(window, 1 << 20) if not m.chunk else min(window, m.chunk)
+    splits = int(max(1, min(splits, (reach + m.keep_first + 31) // 32 + 1)))
     partial = ctx.scratch("attn.partial", (nt, m.nh, splits, m.dv + 2), torch.float32) if splits > 1 else None
     lib.call("tb_attention_window_" + sfx, lib.ptr(z), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v), lib.ptr(gate),
              lib.ptr(tiles.seq), lib.ptr(tiles.t0), lib.ptr(tiles.nq), lib.ptr(ctx.tok_pos), lib.ptr(table),
-             lib.ptr(partial), tiles.count, nt, ctx.max_pages, m.qkv_width, m.qkv_width, m.nh, m.nkvh, m.dh, m.dv,
-             splits, window, m.keep_first, m.scale, m.softcap)
+             lib.ptr(partial), tiles.count, nt, ctx.max_pages, q_stride, m.qkv_width, m.nh, m.nkvh, m.dh, m.dv,
+             splits, window, m.keep_first, m.scale, m.softcap, m.chunk, lib.ptr(sinks), lib.ptr(ocos), lib.ptr(osin))

@@ -25,7 +25,14 @@ Position      owned by the mixer that uses it.  A rotary encoding answers ``rota
               change the step's queries and keys in place by its own means.
 Head          ``forward(ctx, xn, logits)``: float logits [rows, vocab] of the normed rows ``xn``.
 Arrangement   how a layer's parts are put together in a block: built from a LayerSpec,
-              ``parts()`` (name -> part), ``mixer``, ``forward(ctx, x, pending, cache, state)``.
+              ``parts()`` (name -> part), ``mixer``, ``forward(ctx, x, pending, cache, state)``.  An
+              arrangement whose parts other than the mixer carry state per sequence offers ``state_needs()``
+              (name -> StateNeed) and is handed ``state`` as a dict of the same names.
+InputFilter   changes what a part reads, row by row or along time: ``forward(ctx, y, out, state)`` with
+              ``y`` the normed rows [nt, d]; it may carry per-sequence state (``state_need()``).
+Joint         rewrites the whole residual stream between two runs of the model: ``begin(ctx, x)`` right after
+              the embedding (to keep what it needs of it), ``forward(ctx, x, pending)`` before the run that
+              names it (``pending`` is what the run before left to be added; it returns what is still pending).
 ============  ===================================================================================
 
 All parts declare their parameters with :meth:`Part.parameters` (name -> shape, role, init) and
@@ -80,6 +87,15 @@ class WeightedRows:
     index: torch.Tensor       # int32 [nt * k]
     weights: torch.Tensor     # float [nt, k]
     k: int
+
+
+@dataclass
+class PairDelta:
+    """Two parts' outputs that are still to be added to the stream together:  x += (first + second), summed in
+    float.  Left by a block whose mixer and feed-forward read the same stream.  A norm that sets
+    ``takes_pair_delta`` does the sum in its own kernel; for any other the block adds it to the stream first."""
+    first: torch.Tensor       # [nt, d]
+    second: Optional[torch.Tensor]
 
 
 @dataclass
@@ -140,6 +156,7 @@ class NormTail:
 class Norm(Part):
     takes_weighted_rows = False
     takes_normed_delta = False
+    takes_pair_delta = False
     can_warm = False           # forward takes ``warm=``: a weight of the next part to fetch into L2 meanwhile
     tails: tuple = ()          # kinds of NormTail that forward(..., tail=) computes along the way
 
@@ -167,6 +184,22 @@ class FeedForward(Part):
     def forward(self, ctx, x1, out):
         """Write the contribution into ``out`` and return None, or return a :class:`WeightedRows`
         that stands for it (``out`` is then left alone)."""
+        raise NotImplementedError
+
+
+class InputFilter(Part):
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def forward(self, ctx, y, out, state) -> None:
+        raise NotImplementedError
+
+
+class Joint(Part):
+    def begin(self, ctx, x) -> None:
+        """Called once per step with the embedding output ``x`` (float [nt, d]), before any layer runs."""
+
+    def forward(self, ctx, x, pending):
         raise NotImplementedError
 
 
@@ -233,4 +266,6 @@ NORMS = Registry("norm")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 POSITIONS = Registry("position encoding")
+INPUT_FILTERS = Registry("input filter")
+JOINTS = Registry("joint")
 ARRANGEMENTS = Registry("block arrangement")     # kind -> class(LayerSpec, dtype, device); see parts/block.py

@@ -17,7 +17,7 @@ return value is what this block leaves.  A block that wants its sums done at onc
 """
 from __future__ import annotations
 
-from .base import ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, NormedDelta, WeightedRows
+from .base import ARRANGEMENTS, FEED_FORWARDS, INPUT_FILTERS, MIXERS, NORMS, NormedDelta, PairDelta, WeightedRows
 
 
 def build_layer(spec, dtype, device):
@@ -159,6 +159,93 @@ class SandwichLayer:
         return None
 
 
+@ARRANGEMENTS.register("parallel")
+class ParallelLayer:
+    """A block whose mixer and feed-forward read the same stream, each through a norm of its own:
+
+        x += mixer(f(norm_m(x))) + feed_forward(norm_f(x))
+
+    ``f`` is an optional input filter of the mixer's side, named "mixer_input_filter" in ``LayerSpec.extra`` (a
+    causal convolution over time, with per-sequence state).  A layer may have no feed-forward.  The two norms share
+    their statistic: one kernel adds what the block before left pending (a pair of outputs, summed in float),
+    and writes both normed rows.  The block leaves its own two outputs pending as a :class:`PairDelta`."""
+
+    def __init__(self, spec, dtype, device):
+        if spec.mixer_norm is None:
+            raise ValueError("the parallel arrangement needs a norm before the mixer")
+        extra = dict(spec.extra)
+        self.spec = spec
+        self.mixer_norm = NORMS.build(spec.mixer_norm, dtype, device)
+        self.mixer = MIXERS.build(spec.mixer, dtype, device)
+        self.filter = INPUT_FILTERS.build(extra["mixer_input_filter"], dtype, device) \
+            if "mixer_input_filter" in extra else None
+        self.feed_forward = self.feed_forward_norm = None
+        if spec.feed_forward is not None:
+            if spec.feed_forward_norm is None:
+                raise ValueError("a parallel block with a feed-forward needs its norm")
+            self.feed_forward_norm = NORMS.build(spec.feed_forward_norm, dtype, device)
+            self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, dtype, device)
+        # both norms in one kernel: two plain RMS norms over the same row with the same eps
+        self._fused = all(n is None or (type(n).__name__ == "RMSNorm") for n in (self.mixer_norm, self.feed_forward_norm)) \
+            and (self.feed_forward_norm is None or self.feed_forward_norm.eps == self.mixer_norm.eps)
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(p.graph_safe for p in self.parts().values())
+
+    @property
+    def launches_only(self) -> bool:
+        return all(p.launches_only for p in self.parts().values())
+
+    def parts(self):
+        out = {"mixer_norm": self.mixer_norm, "mixer": self.mixer}
+        if self.filter is not None:
+            out["mixer_input_filter"] = self.filter
+        if self.feed_forward is not None:
+            out.update({"feed_forward_norm": self.feed_forward_norm, "feed_forward": self.feed_forward})
+        return out
+
+    def state_needs(self):
+        """Per-sequence state by the name of the part that carries it."""
+        out = {}
+        if self.mixer.state_need() is not None:
+            out["mixer"] = self.mixer.state_need()
+        if self.filter is not None and self.filter.state_need() is not None:
+            out["mixer_input_filter"] = self.filter.state_need()
+        return out
+
+    def forward(self, ctx, x, pending, cache_view, state):
+        from .norm import pair_add_rmsnorm
+        nt, d = x.shape
+        state = state or {}
+        h1 = ctx.scratch("block.x1", (nt, d), ctx.dtype)
+        h2 = ctx.scratch("block.x2", (nt, d), ctx.dtype) if self.feed_forward is not None else None
+        out_m = ctx.scratch("block.delta", (nt, d), ctx.dtype)
+        out_f = ctx.scratch("block.delta2", (nt, d), ctx.dtype) if self.feed_forward is not None else None
+        if isinstance(pending, (NormedDelta, WeightedRows)):
+            pending = resolve(pending, None, out_m, x=x, ctx=ctx)
+        if self._fused:
+            pair_add_rmsnorm(ctx.dtype, x, pending, None, self.mixer_norm.weights["weight"], h1,
+                             None if h2 is None else self.feed_forward_norm.weights["weight"], h2, self.mixer_norm.eps)
+        else:
+            pending = resolve(pending, self.mixer_norm, out_m, x=x, ctx=ctx)
+            self.mixer_norm.forward(ctx, x, pending, None, h1)
+            if h2 is not None:
+                self.feed_forward_norm.forward(ctx, x, None, None, h2)
+        if self.filter is not None:
+            f1 = ctx.scratch("block.x1f", (nt, d), ctx.dtype)
+            self.filter.forward(ctx, h1, f1, state.get("mixer_input_filter"))
+            h1 = f1
+        self.mixer.forward(ctx, h1, out_m, cache_view, state.get("mixer"))
+        if self.feed_forward is None:
+            return out_m
+        lazy = self.feed_forward.forward(ctx, h2, out_f)
+        if lazy is not None:
+            from .feed_forward import sum_weighted_rows
+            sum_weighted_rows(lazy, out_f)
+        return PairDelta(out_m, out_f)
+
+
 def add_pending(ctx, x, pending) -> None:
     """x += pending, at once and in float, for an arrangement that does not leave the sum to a norm."""
     if pending is None:
@@ -166,6 +253,10 @@ def add_pending(ctx, x, pending) -> None:
     if isinstance(pending, NormedDelta):
         from .norm import post_add_rmsnorm
         post_add_rmsnorm(ctx.dtype, x, pending, None, None, 0.0, None)
+        return
+    if isinstance(pending, PairDelta):
+        from .norm import pair_add_rmsnorm
+        pair_add_rmsnorm(ctx.dtype, x, pending, None, None, None, None, None, 0.0)
         return
     if isinstance(pending, WeightedRows):
         from .feed_forward import sum_weighted_rows
@@ -185,7 +276,14 @@ def resolve(pending, norm, into, x=None, ctx=None):
             raise ValueError("a normed delta can only be resolved with the stream at hand")
         add_pending(ctx, x, pending)
         return None
-    if isinstance(pending, WeightedRows) and not norm.takes_weighted_rows:
+    if isinstance(pending, PairDelta):
+        if getattr(norm, "takes_pair_delta", False):
+            return pending
+        if x is None or ctx is None:
+            raise ValueError("a pair of outputs can only be resolved with the stream at hand")
+        add_pending(ctx, x, pending)
+        return None
+    if isinstance(pending, WeightedRows) and not getattr(norm, "takes_weighted_rows", False):
         from .feed_forward import sum_weighted_rows
         sum_weighted_rows(pending, into)
         return into

@@ -24,7 +24,9 @@ class DenseSwiGLU(FeedForward):
     out = h Wd^T (compute.rs:278-292).  With ``bias`` all three projections have one: ``bgu`` (gate's, then up's)
     and ``bd``, float.  The down projection's bias rides inside its product: the bound weight gets the bias as one
     more column (and zeros up to a multiple of eight), and the kernel that applies the pair's biases and the
-    activation writes a one into that column of ``h``."""
+    activation writes a one into that column of ``h``.  ``glu_limit`` (with ``glu_alpha``, default 1): the pair
+    becomes g' * sigmoid(alpha g') * (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit) instead of
+    silu(g) * u, in the product's epilogue."""
     graph_safe = True
     launches_only = True
 
@@ -33,6 +35,10 @@ class DenseSwiGLU(FeedForward):
         self.d = int(params["width"])
         self.di = int(params["di"])
         self.bias = bool(params.get("bias", False))
+        limit = params.get("glu_limit")
+        self.glu = None if limit is None else (float(params.get("glu_alpha", 1.0)), float(limit))
+        if self.glu is not None and self.bias:
+            raise ValueError("the clamped pair has no form with biases")
 
     def parameters(self):
         decl = {"wgu": ParamDecl((2 * self.di, self.d)), "wd": ParamDecl((self.d, self.di))}
@@ -60,7 +66,7 @@ class DenseSwiGLU(FeedForward):
             matmul_nt(h, self.weights["wd"], out)
             return
         h = ctx.scratch("ff.h", (nt, self.di), self.dtype)
-        grouped_matmul(x1, self.weights["wgu"], h, swiglu=True)
+        grouped_matmul(x1, self.weights["wgu"], h, swiglu=True, glu=self.glu)
         matmul_nt(h, self.weights["wd"], out)
 
 

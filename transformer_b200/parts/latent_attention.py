@@ -11,6 +11,12 @@ Nothing per head is cached or formed for cached tokens: the query goes to the la
 [c | kr] with c as the value as well, and Wuv_h is applied to the attention's result (csrc/latent.cu).
 A layer with ``own_latent`` False makes no latent: it reads the cache of the run named by its
 ``RunEntry.cache_of``, with its own Wuk, Wuv, queries and window.
+
+Variants by parameter: ``q_rank`` 0: the queries come straight from one projection, q = Wq x1 (no low-rank step and
+no query norm; Wq rides in the merged first product); ``window`` 0: plain causal attention; a rotary part with
+adjacent pairs (2i, 2i + 1): the kernels pair entry i with i + dims/2, so the rows of the projections that make
+the rotated entries are reordered once at binding (evens, then odds) -- a permutation applied to queries and
+keys alike, which leaves every score as it was.
 """
 from __future__ import annotations
 
@@ -43,11 +49,18 @@ class LatentAttention(Mixer):
             raise ValueError("latent attention needs the rotary encoding of its rotated part ('position')")
         self.position = POSITIONS.build(pos, dtype, device)
         self.rdims = int(pos.get()["dh"])
-        if self.rdims > self.rot or self.rdims % 2 or pos.get().get("pairing") != "half":
+        self.adjacent = pos.get().get("pairing", "adjacent") == "adjacent"
+        if self.adjacent:       # the tables are the same; the pairing is met by reordering the projections' rows
+            self.position = POSITIONS.build(PartSpec.of("rope", **dict(pos.get(), pairing="half")), dtype, device)
+        if self.rdims > self.rot or self.rdims % 2:
             raise ValueError(f"the rotated part of {self.rot} entries takes a rotation of an even number of them, "
-                             f"halves paired; got {self.rdims}, {pos.get().get('pairing')!r}")
-        if self.window <= 0:
-            raise ValueError(f"the window must hold at least the token itself, got {self.window}")
+                             f"got {self.rdims}")
+        if self.adjacent and not self.own_latent:
+            raise ValueError("adjacent pairs are met in the layer that makes the latent; a reader needs halves paired")
+        if self.window < 0:
+            raise ValueError(f"the window must not be negative, got {self.window}")
+        if self.window == 0:
+            self.window = 1 << 30      # plain causal: the mask never cuts
         if self.rank > 512:
             raise ValueError(f"the latent attention kernel takes latents of up to 512 entries, got {self.rank}")
         self.q_head = self.dim + self.rot
@@ -59,24 +72,43 @@ class LatentAttention(Mixer):
         return self.position.graph_safe
 
     def parameters(self):
-        down = self.q_rank + (self.rank + self.rot if self.own_latent else 0)
+        first = self.q_rank if self.q_rank else self.H * self.q_head
+        down = first + (self.rank + self.rot if self.own_latent else 0)
         decl = {
-            "wdown": ParamDecl((down, self.d)),            # rows: Wdq, then (own latent) Wdkv
-            "q_norm": ParamDecl((self.q_rank,), "norm", "ones"),
-            "uq": ParamDecl((self.H * self.q_head, self.q_rank)),
+            "wdown": ParamDecl((down, self.d)),            # rows: Wdq (or Wq itself without a low-rank step), then (own latent) Wdkv
             "uk": ParamDecl((self.H * self.dim, self.rank)),
             "uv": ParamDecl((self.H * self.vdim, self.rank)),
             "wo": ParamDecl((self.d, self.H * self.vdim)),
         }
+        if self.q_rank:
+            decl["q_norm"] = ParamDecl((self.q_rank,), "norm", "ones")
+            decl["uq"] = ParamDecl((self.H * self.q_head, self.q_rank))
         if self.own_latent:
             decl["c_norm"] = ParamDecl((self.rank,), "norm", "ones")
         return decl
+
+    def _halves(self, rows: torch.Tensor) -> torch.Tensor:
+        """Rows of a rotated part [..., rot, in]: the rotated entries' evens first, then their odds."""
+        r = self.rdims
+        order = list(range(0, r, 2)) + list(range(1, r, 2)) + list(range(r, self.rot))
+        return rows[..., order, :]
 
     def bind(self, tensors) -> None:
         super().bind(tensors)
         # the product that takes the queries to the latent's side wants Wuk_h^T as its [out, in] matrix
         uk = self.weights.pop("uk")
         self.weights["ukT"] = uk.view(self.H, self.dim, self.rank).transpose(1, 2).contiguous()
+        if self.adjacent and self.rdims:
+            qname = "uq" if self.q_rank else "wdown"
+            wq = self.weights[qname].clone()
+            nq = self.H * self.q_head
+            heads = wq[:nq].view(self.H, self.q_head, -1)
+            heads[:, self.dim:] = self._halves(heads[:, self.dim:].clone())
+            if self.own_latent:
+                wd = wq if qname == "wdown" else self.weights["wdown"].clone()
+                wd[-self.rot:] = self._halves(wd[-self.rot:].clone())
+                self.weights["wdown"] = wd
+            self.weights[qname] = wq
 
     def cache_need(self):
         return CacheNeed("latent", 1, self.rank + self.rot, (("rank", self.rank), ("rot", self.rot)))
@@ -88,18 +120,27 @@ class LatentAttention(Mixer):
         wa = w["wdown"].shape[0]
         a = ctx.scratch("latent.a", (nt, wa), self.dtype)
         matmul_nt(x1, w["wdown"], a)
-        cq = ctx.scratch("latent.cq", (nt, self.q_rank), self.dtype)
         table = ctx.page_table(cache)
         cos, sin, _ = self.position.rotation()
         write = self.own_latent and cache.writable
-        lib.call("tb_latent_prep_" + sfx, lib.ptr(a), wa, lib.ptr(w["q_norm"]), lib.ptr(w.get("c_norm")), self.eps,
-                 lib.ptr(cq), lib.ptr(cache.kv) if write else 0, lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos),
-                 lib.ptr(table), ctx.max_pages, lib.ptr(cos), lib.ptr(sin), nt, self.q_rank, self.rank, self.rot,
-                 self.rdims)
-        q = ctx.scratch("latent.q", (nt, H * self.q_head), self.dtype)
-        matmul_nt(cq, w["uq"], q)
+        if self.q_rank:
+            cq = ctx.scratch("latent.cq", (nt, self.q_rank), self.dtype)
+            lib.call("tb_latent_prep_" + sfx, lib.ptr(a), wa, lib.ptr(w["q_norm"]), lib.ptr(w.get("c_norm")), self.eps,
+                     lib.ptr(cq), lib.ptr(cache.kv) if write else 0, lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos),
+                     lib.ptr(table), ctx.max_pages, lib.ptr(cos), lib.ptr(sin), nt, self.q_rank, self.rank, self.rot,
+                     self.rdims)
+            q = ctx.scratch("latent.q", (nt, H * self.q_head), self.dtype)
+            matmul_nt(cq, w["uq"], q)
+        else:
+            # the queries are the first columns of the merged product; the latent's part follows them
+            q = a[:, :H * self.q_head]
+            if write:
+                lib.call("tb_latent_prep_" + sfx, lib.ptr(a[:, H * self.q_head:]), wa, 0, lib.ptr(w.get("c_norm")),
+                         self.eps, 0, lib.ptr(cache.kv), lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(table),
+                         ctx.max_pages, lib.ptr(cos), lib.ptr(sin), nt, 0, self.rank, self.rot, self.rdims)
+        ldq = q.stride(0)
         qa = ctx.scratch("latent.qa", (nt, H, self.rank), self.dtype)
-        batched_matmul(q.view(nt, H, self.q_head)[:, :, :self.dim], w["ukT"], qa)
+        batched_matmul(q.as_strided((nt, H, self.dim), (ldq, self.q_head, 1)), w["ukT"], qa)
         ol = ctx.scratch("latent.ol", (nt, H, self.rank), self.dtype)
         tiles = ctx.tiles(self.tile)
         done = False
@@ -107,17 +148,18 @@ class LatentAttention(Mixer):
             # Slices of the key range, so that a few sequences still fill the GPU: a function of the batch's shape
             # alone (a captured graph keeps it), at most one slice per page of the window
             blocks = tiles.count * ((H + 15) // 16)
-            splits = int(max(1, min(16, (self.window + 63) // 64 + 1, (2 * ctx.engine.sm_count) // max(1, blocks))))
+            splits = int(max(1, min(16, (min(self.window, ctx.engine.spec.max_context) + 63) // 64 + 1,
+                                    (2 * ctx.engine.sm_count) // max(1, blocks))))
             partial = ctx.scratch("latent.partial", (nt, H, splits, self.rank + 2), torch.float32) if splits > 1 else None
             done = lib.try_call("tb_latent_attention_mma_bf16", lib.ptr(qa), lib.ptr(q), lib.ptr(ol), lib.ptr(partial),
                                 lib.ptr(cache.kv), lib.ptr(tiles.seq), lib.ptr(tiles.t0), lib.ptr(tiles.nq),
                                 lib.ptr(ctx.tok_pos), lib.ptr(table), lib.ptr(cos), lib.ptr(sin), tiles.count, nt,
-                                ctx.max_pages, H * self.q_head, self.q_head, H, self.rank, self.rot, self.rdims,
+                                ctx.max_pages, ldq, self.q_head, H, self.rank, self.rot, self.rdims,
                                 self.window, splits, self.scale)
         if not done:
             lib.call("tb_latent_attention_" + sfx, lib.ptr(qa), lib.ptr(q), lib.ptr(ol), lib.ptr(cache.kv),
                      lib.ptr(tiles.seq), lib.ptr(tiles.t0), lib.ptr(tiles.nq), lib.ptr(ctx.tok_pos), lib.ptr(table),
-                     lib.ptr(cos), lib.ptr(sin), tiles.count, ctx.max_pages, H * self.q_head, self.q_head, self.dim, H,
+                     lib.ptr(cos), lib.ptr(sin), tiles.count, ctx.max_pages, ldq, self.q_head, self.dim, H,
                      self.rank, self.rot, self.rdims, self.window, self.scale)
         o = ctx.scratch("latent.o", (nt, H, self.vdim), self.dtype)
         batched_matmul(ol, w["uv"].view(H, self.vdim, self.rank), o)

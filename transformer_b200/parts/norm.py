@@ -2,18 +2,21 @@
 from __future__ import annotations
 
 from ..csrc import lib
-from .base import NORMS, Norm, NormedDelta, ParamDecl, WeightedRows
+from .base import NORMS, Norm, NormedDelta, PairDelta, ParamDecl, WeightedRows
 
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
-    """params: width, eps, mult (default 1).  y = v / rms(v) * weight * mult.  Statistics and the residual sum are
-    float; one rounding at the store.  The multiplier is folded into the bound weight (a float product, once)."""
+    """params: width, eps, mult (default 1), one_plus (default False).  y = v / rms(v) * weight * mult, or with
+    ``one_plus`` (a weight stored around zero) v / rms(v) * (1 + weight) * mult.  Statistics and the residual sum are
+    float; one rounding at the store.  The multiplier and the one are folded into the bound weight (float, once).
+    A :class:`PairDelta` (two parts' outputs, both still to be added) is summed in the same kernel."""
 
     graph_safe = True
     launches_only = True
     takes_weighted_rows = True
     takes_normed_delta = True
+    takes_pair_delta = True
     can_warm = True
     tails = ("router",)
 
@@ -22,18 +25,26 @@ class RMSNorm(Norm):
         self.width = int(params["width"])
         self.eps = float(params["eps"])
         self.mult = float(params.get("mult", 1.0))
+        self.one_plus = bool(params.get("one_plus", False))
 
     def parameters(self):
-        return {"weight": ParamDecl((self.width,), "norm", "ones")}
+        return {"weight": ParamDecl((self.width,), "norm", "normal" if self.one_plus else "ones")}
 
     def bind(self, tensors) -> None:
         super().bind(tensors)
+        if self.one_plus:
+            self.weights["weight"] = self.weights["weight"].float() + 1.0
         if self.mult != 1.0:
             self.weights["weight"] = self.weights["weight"].float() * self.mult
 
     def forward(self, ctx, x, delta, rows, y, warm=None, tail=None) -> None:
         if isinstance(delta, NormedDelta):
             post_add_rmsnorm(self.dtype, x, delta, rows, self.weights["weight"], self.eps, y, tail=tail)
+            return
+        if isinstance(delta, PairDelta):
+            pair_add_rmsnorm(self.dtype, x, delta, rows, self.weights["weight"], y, None, None, self.eps)
+            if tail is not None:
+                _route(lib.suffix(self.dtype), y, tail, y.shape[0], self.width)
             return
         n_out = y.shape[0]
         wy = idx = wts = None
@@ -80,6 +91,7 @@ class NoNorm(Norm):
     launches_only = True
     takes_weighted_rows = True
     takes_normed_delta = True
+    takes_pair_delta = True
 
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)
@@ -88,6 +100,9 @@ class NoNorm(Norm):
     def forward(self, ctx, x, delta, rows, y) -> None:
         if isinstance(delta, NormedDelta):
             post_add_rmsnorm(self.dtype, x, delta, rows, None, 0.0, y)
+            return
+        if isinstance(delta, PairDelta):
+            pair_add_rmsnorm(self.dtype, x, delta, rows, None, y, None, None, 0.0)
             return
         wy = idx = wts = None
         k = 0
@@ -127,3 +142,18 @@ def post_add_rmsnorm(dtype, x, pending: NormedDelta, rows, weight, eps, y, tail=
              lib.ptr(y), n_out, x.shape[1])
     if tail is not None:
         _route(sfx, y, tail, n_out, x.shape[1])
+
+
+def pair_add_rmsnorm(dtype, x, pending, rows, w1, y1, w2, y2, eps) -> None:
+    """x[rows] += pending.first + pending.second (float; written back when ``rows`` is None; ``pending`` may be a
+    tensor, a :class:`PairDelta` or None), then y1 = x / rms(x) * w1 and y2 = x / rms(x) * w2: one statistic, two
+    weights.  A null weight gives the sum itself, rounded once; a null output is left out."""
+    d1 = d2 = None
+    if isinstance(pending, PairDelta):
+        d1, d2 = pending.first, pending.second
+    elif pending is not None:
+        d1 = pending
+    n_out = x.shape[0] if rows is None else rows.shape[0]
+    lib.call("tb_pair_add_rmsnorm_" + lib.suffix(dtype), lib.ptr(x), lib.ptr(d1), lib.ptr(d2), lib.ptr(rows), lib.ptr(w1),
+             lib.ptr(y1), 0 if y1 is None else y1.stride(0), lib.ptr(w2), lib.ptr(y2), 0 if y2 is None else y2.stride(0),
+             float(eps), n_out, x.shape[1])

@@ -11,6 +11,8 @@ which architecture it came from.
 * ``ModelSpec.order`` is the run order: a list of :class:`RunEntry`.  It may name a layer twice
   (weights shared, each run with a cache entry of its own unless told otherwise) or let a run read
   the cache that another run wrote (``cache_of``).
+* ``ModelSpec.joints`` are parts that rewrite the whole residual stream between two runs (a projection that
+  mixes the embedding output back in, ...); a :class:`RunEntry` names the one that runs right before it.
 """
 from __future__ import annotations
 
@@ -45,6 +47,7 @@ class LayerSpec:
 class RunEntry:
     layer: int                      # index into ModelSpec.layers
     cache_of: Optional[int] = None  # index into ModelSpec.order whose cache this run reads and does not write
+    joint: Optional[int] = None     # index into ModelSpec.joints of the part that rewrites the stream right before this run
 
 
 @dataclass(frozen=True)
@@ -58,6 +61,7 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     stop_tokens: Tuple[int, ...] = ()
+    joints: Tuple[PartSpec, ...] = ()
 
     def validate(self) -> None:
         if not self.layers:
@@ -65,6 +69,8 @@ class ModelSpec:
         for i, e in enumerate(self.order):
             if not (0 <= e.layer < len(self.layers)):
                 raise ValueError(f"run entry {i} names layer {e.layer}, but there are {len(self.layers)}")
+            if e.joint is not None and not (0 <= e.joint < len(self.joints)):
+                raise ValueError(f"run entry {i} names joint {e.joint}, but there are {len(self.joints)}")
             if e.cache_of is not None:
                 if not (0 <= e.cache_of < i):
                     raise ValueError(f"run entry {i} reads the cache of entry {e.cache_of}, which must come earlier")
