@@ -196,6 +196,38 @@ def zufadra_shapes(size):
     return zufadra, llama
 
 
+def dumalix_shapes(size):
+    """(Dumalix config, Zufadra config of windowed attention alone, Salepel config) for a named size.  The Dumalix
+    layers alternate between the latent attention and the chunked attention, each beside the clamped dense
+    feed-forward; one pass over a repeated group of two layers.  The Zufadra model has the same width, depth, heads,
+    head sizes and feed-forward, every layer a windowed attention (window = the chunk): the closest model for the
+    attention kernels, the products and the feed-forward.  The Salepel model of the same size names has latents and
+    heads of the same sizes: the closest model for the latent attention's kernels."""
+    d, L, H, G, dim, chunk, lat_dim, rot, rank, ff = {
+        "s": (1024, 8, 8, 2, 128, 1024, 64, 32, 256, 2816),
+        "m": (2048, 8, 16, 4, 128, 2048, 128, 64, 512, 5632),
+    }[size]
+    att = {"heads": H, "kv_heads": G, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "conv": 4, "mask": {"size": chunk},
+           "rot": {"base": 500000.0, "dims": dim // 2,
+                   "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+    lat = {"heads": H, "dim": lat_dim, "rot_dim": rot, "vdim": lat_dim, "kv_rank": rank, "scale": (lat_dim + rot) ** -0.5,
+           "rot": {"base": 10000.0, "dims": rot, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    layers = [{"type": "latent_attention" if i % 2 == 0 else "attention", "mixer": lat if i % 2 == 0 else att, "mlp": mlp}
+              for i in range(L)]
+    dumalix = {"architecture": "Dumalix", "vocab": 32000, "width": d, "norm": {"eps": 1e-6}, "canon": {"taps": 4},
+               "loop": {"start": 2, "stop": 4, "times": 1}, "max_context": 8192, "layers": layers}
+    zatt = {"heads": H, "kv_heads": G, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 30.0,
+            "mask": {"size": chunk, "keep_first": 4},
+            "rot": {"base": 500000.0, "dims": dim // 2,
+                    "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    zufadra = {"architecture": "Zufadra", "vocab": 32000, "width": d, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+               "logit_scale": 0.5, "embedding": {"scale": 8.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+               "max_context": 8192,
+               "layers": [{"type": "attention", "mixer": zatt, "mlp": {"kind": "dense", "ff": ff}} for _ in range(L)]}
+    return dumalix, zufadra, design_shapes(size)[0]
+
+
 def bench_design(args):
     """Prefill and decode throughput of another design beside the closest existing model of equal sizes, and the
     device time of every kernel family in one eager step of each (CUDA events around each launch).  One JSON line."""
@@ -208,8 +240,9 @@ def bench_design(args):
     T, B, ctx0, K, W = args.prefill_tokens, args.batch, 1024, args.steps, max(3, args.warmup)
     gen = torch.Generator().manual_seed(7)
     names, shapes = {"salepel": (("salepel", "llama_moe"), design_shapes),
-                     "zufadra": (("zufadra", "llama_dense"), zufadra_shapes)}[args.design]
-    out = {"metric": f"prefill and decode tok/s, {names[0]} beside {names[1]} at equal sizes", "unit": "tokens/s",
+                     "zufadra": (("zufadra", "llama_dense"), zufadra_shapes),
+                     "dumalix": (("dumalix", "zufadra_attention", "salepel"), dumalix_shapes)}[args.design]
+    out = {"metric": f"prefill and decode tok/s, {names[0]} beside {' and '.join(names[1:])} at equal sizes", "unit": "tokens/s",
            "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic: random weights, random token ids",
            "peaks": pk, "prefill_tokens": T, "decode_batch": B, "decode_context": ctx0, "steps": K, "warmup": W,
            "sizes": {}}
@@ -304,7 +337,7 @@ def main():
                     help="layer sizes: the benchmark's (default) or another shape BASELINE.json names")
     ap.add_argument("--prompt-max", type=int, default=0, help="longest prompt drawn (default: the shape's own)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
-    ap.add_argument("--design", default=None, choices=["salepel", "zufadra"],
+    ap.add_argument("--design", default=None, choices=["salepel", "zufadra", "dumalix"],
                     help="instead of the default workload: this design beside the closest existing model at equal "
                          "sizes (prefill of --prefill-tokens, decode at --batch; sizes from --sizes)")
     ap.add_argument("--sizes", default="s,m", help="with --design: which of the named sizes (s, m)")

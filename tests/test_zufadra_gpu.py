@@ -295,12 +295,12 @@ def _window_attention(dtype, nh, nkvh, dk, dv, window, keep, cap, lens_before, l
     if kernel == "general":
         lib.call("tb_attention_window_" + sfx, lib.ptr(d_z), lib.ptr(out), lib.ptr(d_kc), lib.ptr(d_vc), lib.ptr(d_gate),
                  lib.ptr(d_seq), lib.ptr(d_t0), lib.ptr(d_nq), lib.ptr(d_pos), lib.ptr(d_table), lib.ptr(partial),
-                 len(tile_seq), nt, max_pages, width, width, nh, nkvh, dk, dv, splits, window, keep, scale, cap)
+                 len(tile_seq), nt, max_pages, width, width, nh, nkvh, dk, dv, splits, window, keep, scale, cap, 0, 0, 0, 0)
     else:
         ok = lib.try_call("tb_attention_window_mma_bf16", lib.ptr(d_z), lib.ptr(out), lib.ptr(d_kc), lib.ptr(d_vc),
                           lib.ptr(d_gate), lib.ptr(d_seq), lib.ptr(d_t0), lib.ptr(d_nq), lib.ptr(d_pos),
                           lib.ptr(d_table), lib.ptr(partial), len(tile_seq), nt, max_pages, width, width, nh, nkvh, dk,
-                          dv, splits, window, keep, scale, cap)
+                          dv, splits, window, keep, scale, cap, 0, 0, 0, 0)
         assert ok, "the tensor-core kernel refused sizes it is meant to take"
     torch.cuda.synchronize()
     want = torch.zeros(nt, nh, dv, dtype=torch.float64)

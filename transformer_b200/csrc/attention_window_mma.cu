@@ -1,7 +1,8 @@
 // Windowed attention over the paged cache on the tensor cores, bfloat16: prompts, portions of prompts and decoding.
 //
 // Same mathematics as the general windowed kernel (attention_window.cu):
-//   score = cap(q . k * scale), visible iff j <= p and (p - j < window or j < keep_first), softmax in float,
+//   score = cap(q . k * scale), visible iff j <= p and (p - j < window or j < keep_first) and (no chunks or both in
+//   the same chunk), an optional sink per head in the denominator, an optional turning back of the output's pairs, softmax in float,
 //   out = softmax . v * sigmoid(gate); key heads of DK and value heads of DV entries.
 //
 // A block = one tile of query tokens of ONE sequence x ONE key/value head with ALL the query heads of its group:
@@ -36,6 +37,10 @@ struct WinMmaArgs {
     const int* tok_pos;
     const int* page_table;
     float* partial;              // [nt, nh, splits, DV + 2] when splits > 1
+    const float* sinks;          // [nh] or null: a number per head in the softmax's denominator
+    const float* ocos;           // [positions, DV / 2] or null: the output's pairs (2m, 2m + 1) are turned back
+    const float* osin;
+    int chunk;                   // > 0: position i sees j only if i / chunk == j / chunk
     int tiles, max_pages, q_stride, gate_stride, nh, nkvh, splits, window, keep_first;
     float scale, softcap;
 };
@@ -67,7 +72,8 @@ __global__ void __launch_bounds__(WM_THREADS, wm_blocks(DK, DV)) attention_windo
     const bool active = warp * 16 < rows;              // this warp's rows hold queries
 
     // the pages to visit
-    const int win_lo = a.window > pos_first ? 0 : pos_first - a.window + 1;
+    int win_lo = a.window > pos_first ? 0 : pos_first - a.window + 1;
+    if (a.chunk > 0) win_lo = max(win_lo, pos_first / a.chunk * a.chunk);     // nothing before the first row's chunk
     const int win_p0 = win_lo / WM_KEYS, win_p1 = pos_last / WM_KEYS + 1;
     const int kept = min(a.keep_first, pos_last + 1);
     const int first = min((kept + WM_KEYS - 1) / WM_KEYS, win_p0);
@@ -158,7 +164,8 @@ __global__ void __launch_bounds__(WM_THREADS, wm_blocks(DK, DV)) attention_windo
             // every key of the page visible to every row of the block: not later than the first row's token, and
             // inside the last row's window or among the kept
             const bool open = key0 + WM_KEYS - 1 <= pos_first &&
-                              (pos_last - key0 < a.window || key0 + WM_KEYS - 1 < a.keep_first);
+                              (pos_last - key0 < a.window || key0 + WM_KEYS - 1 < a.keep_first) &&
+                              (a.chunk <= 0 || key0 / a.chunk == pos_last / a.chunk);
             float mx[2] = {m_run[0], m_run[1]};
 #pragma unroll
             for (int nb = 0; nb < WM_KEYS / 8; ++nb) {
@@ -170,7 +177,9 @@ __global__ void __launch_bounds__(WM_THREADS, wm_blocks(DK, DV)) attention_windo
                     if (!open) {
                         const int key = key0 + nb * 8 + tid4 * 2 + (c & 1);
                         const int pos = (c & 2) ? pos_b : pos_a;
-                        if (key > pos || (pos - key >= a.window && key >= a.keep_first)) v = -INFINITY;
+                        if (key > pos || (pos - key >= a.window && key >= a.keep_first) ||
+                            (a.chunk > 0 && key / a.chunk != pos / a.chunk))
+                            v = -INFINITY;
                     }
                     s[nb][c] = v;
                     mx[c >> 1] = fmaxf(mx[c >> 1], v);
@@ -238,12 +247,30 @@ __global__ void __launch_bounds__(WM_THREADS, wm_blocks(DK, DV)) attention_windo
         const int tq = row / group, hh = row - tq * group;
         const int t = t0 + tq, h = g * group + hh;
         if (a.splits == 1) {
-            const float inv = 1.0f / l_run[r];
+            float lsum = l_run[r], keep = 1.f;
+            if (a.sinks) {      // the larger of the sink and the running maximum stays the reference
+                const float sk = a.sinks[h] * LOG2E;
+                if (sk > m_run[r]) {
+                    keep = exp2f(m_run[r] - sk);
+                    lsum = lsum * keep + 1.f;
+                } else {
+                    lsum += exp2f(sk - m_run[r]);
+                }
+            }
+            const float inv = keep / lsum;
+            const float* oc = a.ocos ? a.ocos + (size_t)a.tok_pos[t] * (DV / 2) + tid4 : nullptr;
+            const float* os = a.ocos ? a.osin + (size_t)a.tok_pos[t] * (DV / 2) + tid4 : nullptr;
             __nv_bfloat16* dst = a.out + ((size_t)t * a.nh + h) * DV + tid4 * 2;
             const __nv_bfloat16* gt = a.gate ? a.gate + (size_t)t * a.gate_stride + (size_t)h * DV + tid4 * 2 : nullptr;
 #pragma unroll
             for (int i = 0; i < DV / 8; ++i) {
                 float v0 = o[i][2 * r] * inv, v1 = o[i][2 * r + 1] * inv;
+                if (oc) {       // this thread holds the pair (2m, 2m + 1), m = 4 i + tid4
+                    const float co = oc[i * 4], si = os[i * 4];
+                    const float r0 = v0 * co + v1 * si, r1 = v1 * co - v0 * si;
+                    v0 = r0;
+                    v1 = r1;
+                }
                 if (gt) {
                     const float2 gg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gt + i * 8));
                     v0 = __fdividef(v0, 1.0f + __expf(-gg.x));
@@ -269,13 +296,15 @@ __global__ void __launch_bounds__(WM_THREADS, wm_blocks(DK, DV)) attention_windo
 // the merge of attention_window.cu, for bfloat16 outputs
 __global__ void attention_window_mma_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
                                                   const __nv_bfloat16* __restrict__ gate, int gate_stride, int nh, int dv,
-                                                  int splits) {
+                                                  int splits, const float* __restrict__ sinks,
+                                                  const float* __restrict__ ocos, const float* __restrict__ osin,
+                                                  const int* __restrict__ tok_pos) {
     pdl_sync();
     const int t = blockIdx.x, h = blockIdx.y;
     const float* p = partial + ((size_t)t * nh + h) * splits * (dv + 2);
-    float m = -INFINITY;
+    float m = sinks ? sinks[h] : -INFINITY;
     for (int s = 0; s < splits; ++s) m = fmaxf(m, p[s * (dv + 2) + dv]);
-    float den = 0.f;
+    float den = sinks ? expf(sinks[h] - m) : 0.f;
     for (int s = 0; s < splits; ++s) {
         const float ms = p[s * (dv + 2) + dv];
         if (ms != -INFINITY) den += p[s * (dv + 2) + dv + 1] * expf(ms - m);
@@ -287,6 +316,16 @@ __global__ void attention_window_mma_merge_kernel(const float* __restrict__ part
             if (ms != -INFINITY) acc += p[s * (dv + 2) + c] * expf(ms - m);
         }
         float v = acc / den;
+        if (ocos) {             // turn the pair (c, c ^ 1) back: the other entry is summed here as well
+            float other = 0.f;
+            for (int s = 0; s < splits; ++s) {
+                const float ms = p[s * (dv + 2) + dv];
+                if (ms != -INFINITY) other += p[s * (dv + 2) + (c ^ 1)] * expf(ms - m);
+            }
+            other /= den;
+            const float co = ocos[(size_t)tok_pos[t] * (dv / 2) + (c >> 1)], si = osin[(size_t)tok_pos[t] * (dv / 2) + (c >> 1)];
+            v = (c & 1) ? v * co - other * si : v * co + other * si;
+        }
         if (gate) v *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)t * gate_stride + (size_t)h * dv + c])));
         out[((size_t)t * nh + h) * dv + c] = __float2bfloat16_rn(v);
     }
@@ -308,7 +347,7 @@ static int window_mma_launch(const WinMmaArgs& a, int nt, cudaStream_t s) {
     if (rc || a.splits == 1) return rc;
     dim3 mgrid(nt, a.nh);
     TB_LAUNCH(attention_window_mma_merge_kernel, mgrid, DV < 128 ? 64 : 128, 0, s, a.partial, a.out, a.gate, a.gate_stride,
-              a.nh, DV, a.splits);
+              a.nh, DV, a.splits, a.sinks, a.ocos, a.osin, a.tok_pos);
     return tb_last_error();
 }
 
@@ -325,8 +364,10 @@ int tb_attention_window_mma_bf16(const void* q, void* out, const void* kc, const
                                  const int* tile_seq, const int* tile_t0, const int* tile_nq, const int* tok_pos,
                                  const int* page_table, float* partial, int tiles, int nt, int max_pages, int q_stride,
                                  int gate_stride, int nh, int nkvh, int dk, int dv, int splits, int window,
-                                 int keep_first, float scale, float softcap, cudaStream_t s) {
+                                 int keep_first, float scale, float softcap, int chunk, const float* sinks,
+                                 const float* ocos, const float* osin, cudaStream_t s) {
     if (nh <= 0 || nkvh <= 0 || nh % nkvh || tiles < 0 || window <= 0 || keep_first < 0 || splits < 1) return TB_ERR_ARG;
+    if (chunk < 0 || (ocos && !osin)) return TB_ERR_ARG;
     if (splits > 1 && !partial) return TB_ERR_ARG;
     if (nh / nkvh > WM_ROWS) return TB_ERR_UNSUPPORTED;
     if (q_stride % 8 || gate_stride % 8 ||
@@ -334,10 +375,12 @@ int tb_attention_window_mma_bf16(const void* q, void* out, const void* kc, const
         return TB_ERR_UNSUPPORTED;
     if (tiles == 0) return 0;
     WinMmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
-                 (const __nv_bfloat16*)gate, tile_seq, tile_t0, tile_nq, tok_pos, page_table, partial, tiles, max_pages,
+                 (const __nv_bfloat16*)gate, tile_seq, tile_t0, tile_nq, tok_pos, page_table, partial, sinks, ocos, osin,
+                 chunk, tiles, max_pages,
                  q_stride, gate_stride, nh, nkvh, splits, window, keep_first, scale, softcap};
 #define WM_CASE(K, V) if (dk == K && dv == V) return window_mma_launch<K, V>(a, nt, s);
     WM_CASE(32, 32)
+    WM_CASE(48, 48)
     WM_CASE(64, 64)
     WM_CASE(96, 96)
     WM_CASE(128, 128)

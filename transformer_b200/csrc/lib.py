@@ -68,7 +68,7 @@ _SIGNATURES: Dict[str, str] = {
     "tb_conv_roll_f32": "piplppiii", "tb_conv_roll_bf16": "piplppiii",
     "tb_causal_conv_f32": "pipplpipppiiiiii", "tb_causal_conv_bf16": "pipplpipppiiiiii",
     "tb_head_prep_f32": "pipplpppfppppppppppppiiiiiiiii", "tb_head_prep_bf16": "pipplpppfppppppppppppiiiiiiiii",
-    "tb_attention_window_mma_bf16": "pppppppppppiiiiiiiiiiiiff",
+    "tb_attention_window_mma_bf16": "pppppppppppiiiiiiiiiiiiffippp",
     "tb_delta_prep_f32": "pipppppppppppiiiiiiii",
     "tb_delta_prep_bf16": "pipppppppppppiiiiiiii",
     "tb_delta_scan": "ppppppiiiiiii",

@@ -330,18 +330,19 @@ def run_window_attention(ctx, m, z, o, gate, cache, table, nt, window, q_stride=
     ``sinks``: a number per head in the softmax's denominator; ``ocos, osin``: tables that turn the output back."""
     sfx = lib.suffix(m.dtype)
     q_stride = m.qkv_width if q_stride is None else q_stride
-    plain = sinks is None and ocos is None and not m.chunk
-    if m.window_tile and USE_WINDOW_MMA and plain:
+    if m.window_tile and USE_WINDOW_MMA:
         # bfloat16: the tensor-core kernel, for prompts and decoding alike.  Slices of the visited pages so that a few
         # sequences still fill the GPU: a function of the batch's shape alone (a captured graph keeps it)
         tiles = ctx.tiles(m.window_tile)
-        pages = (min(window, ctx.engine.spec.max_context) + m.keep_first + 63) // 64 + 2
+        reach = min(window, ctx.engine.spec.max_context) if not m.chunk else min(window, m.chunk)
+        pages = (reach + m.keep_first + 63) // 64 + 2
         splits = int(max(1, min(16, pages, (2 * ctx.engine.sm_count) // max(1, tiles.count * m.nkvh))))
         partial = ctx.scratch("attn.partial", (nt, m.nh, splits, m.dv + 2), torch.float32) if splits > 1 else None
         if lib.try_call("tb_attention_window_mma_bf16", lib.ptr(z), lib.ptr(o), lib.ptr(cache.k), lib.ptr(cache.v),
                         lib.ptr(gate), lib.ptr(tiles.seq), lib.ptr(tiles.t0), lib.ptr(tiles.nq), lib.ptr(ctx.tok_pos),
                         lib.ptr(table), lib.ptr(partial), tiles.count, nt, ctx.max_pages, q_stride, m.qkv_width,
-                        m.nh, m.nkvh, m.dh, m.dv, splits, window, m.keep_first, m.scale, m.softcap):
+                        m.nh, m.nkvh, m.dh, m.dv, splits, window, m.keep_first, m.scale, m.softcap, m.chunk,
+                        lib.ptr(sinks), lib.ptr(ocos), lib.ptr(osin)):
             return
     tiles = ctx.tiles(m.general_tile)
     # slices of the visited keys so that a few sequences still fill the GPU: a function of the batch's shape alone (a
