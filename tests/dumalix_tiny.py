@@ -17,8 +17,10 @@ def rot(base, dims, scaling=None):
 
 
 def attention(heads, kv_heads, dim, vdim, conv=3, chunk=None, dims=None, base=10000.0, scaling=None, scale=None):
-    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv,
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
          "rot": rot(base, dim if dims is None else dims, scaling), "scale": dim ** -0.5 if scale is None else scale}
+    if conv is not None:        # absent: no convolution on the projections; 1: a weight per channel
+        m["conv"] = conv
     if chunk is not None:
         m["mask"] = {"size": chunk}
     return {"type": "attention", "mixer": m}
@@ -46,7 +48,7 @@ def config(vocab, width, layers, eps=1e-6, taps=3, loop=None):
 
 # Sizes differ from one another wherever the design lets them: query and key heads, the two head sizes, groups of
 # one and of several, a rotation of a part of the head and of all of it, rescaled frequencies with the ramp inside
-# the head, chunks shorter than a page and across page borders or none, two to five taps, layers with and without
+# the head, chunks shorter than a page and across page borders or none, one to five taps or no convolution, layers with and without
 # a feed-forward, a repeated group at the start, in the middle and up to the end, three passes, one, or no loop.
 MIXED = config(101, 64, [
     (latent(3, 16, 8, 12, 24, base=5000.0, scaling=(4.0, 64, 8.0, 1.0), scale=0.2), dense(48, 0.8)),
@@ -63,7 +65,7 @@ WIDE = config(128, 128, [
     (attention(4, 2, 64, 64, conv=4, chunk=100, dims=32, scaling=(3.0, 256, 8.0, 1.0)), dense(96)),
     (latent(4, 64, 32, 64, 64, scaling=(4.0, 256, 16.0, 1.0)), None),
     (attention(8, 2, 128, 64, conv=2, chunk=64, dims=64, base=5e5), dense(96, 3.0)),
-    (attention(2, 2, 32, 32, conv=3, dims=32), None),
+    (attention(2, 2, 32, 32, conv=None, dims=32), None),
     (latent(8, 32, 16, 32, 96), dense(64)),
 ], taps=2, loop=(2, 5, 2))
 # sizes that are multiples of nothing: every vectorized or tensor-core form refuses them
@@ -103,10 +105,10 @@ def random_tensors(cfg, seed, std=0.15):
             mat(p + "canon1", d, taps, s=0.4)
         H = m["heads"]
         if layer["type"] == "attention":
-            G, T = m["kv_heads"], m["conv"]
+            G, T = m["kv_heads"], m.get("conv", 0)
             for n, rows in (("q", H * m["dim"]), ("k", G * m["dim"]), ("v", G * m["vdim"])):
                 mat(p + "mix." + n, rows, d, s=2 * std)
-                if T > 1:
+                if T:
                     mat(p + f"mix.{n}.conv", rows, T, s=0.6)
             around(p + "mix.q.norm", m["dim"], 1.3)          # scores that matter, and that bfloat16 can still carry
             around(p + "mix.k.norm", m["dim"], 1.0)
@@ -144,13 +146,16 @@ def make_folder(tmp, name, tensors_edit=None):
 
 
 FP32_TOL = 2e-4           # on logits of order one to ten
-# The 16-bit path against the plain implementation rounding where that path stores an activation, as parts of the
-# largest |logit| of the request: no position further off than 2^-4, and the positions on average within 2^-6 (the
-# rounding of single products differs between kernels and piles up in single entries, not in the mean).  A wrong
-# mechanism (a chunk one token off, a lost state, a missing sink) moves the logits by a tenth of their size or more,
-# and the 32-bit path holds every position to FP32_TOL.
-BF16_REL_TOL = 2.0 ** -4
-BF16_MEAN_TOL = 2.0 ** -6
+# The 16-bit path is measured against what 16-bit storage itself costs in this model: the plain implementation run
+# exactly and run again rounding where the 16-bit path stores an activation.  The largest difference of the two over
+# a position's logits, its maximum and its mean over the request's positions, is the floor.  No position of the
+# engine may be further from the exact logits than twice the floor's maximum, and the positions on average not
+# further than one and a half times its mean: the engine rounds at the same places, so it sits at the floor (both
+# ratios were between 1.0 and 1.2 whichever kernels ran), while a wrong mechanism (a chunk one token off, a lost
+# state, a missing sink) moves most positions by several floors.  The 32-bit path holds every position to FP32_TOL.
+BF16_MAX_FLOORS = 2.0
+BF16_MEAN_FLOORS = 1.5
+BF16_REL_TOL = 2.0 ** -4  # two runs of the 16-bit path against one another, as a part of the largest |logit|
 
 
 def as_bfloat16(x):
@@ -159,18 +164,22 @@ def as_bfloat16(x):
 
 def check_request(cfg, tensors, tokens, got_rows, dtype, label=""):
     """got_rows: {position: logits row of the engine}.  Every position must be within the rule of the path."""
-    ref = DP.forward(cfg, tensors, tokens, store=as_bfloat16 if dtype == "bfloat16" else None)
-    top = float(ref.abs().max())
-    tol = FP32_TOL * max(1.0, top / 10.0) if dtype == "float32" else BF16_REL_TOL * top
+    ref = DP.forward(cfg, tensors, tokens)
+    if dtype == "float32":
+        tol = FP32_TOL * max(1.0, float(ref.abs().max()) / 10.0)
+    else:
+        floor = (DP.forward(cfg, tensors, tokens, store=as_bfloat16) - ref).abs().max(dim=1).values
+        # a request of a few positions has a floor of a few samples: never below 2^-5 of the largest |logit|
+        tol = max(BF16_MAX_FLOORS * float(floor.max()), 2.0 ** -5 * float(ref.abs().max()))
     worst, total = 0.0, 0.0
     for pos, row in sorted(got_rows.items()):
         diff = float((torch.as_tensor(row).double() - ref[pos]).abs().max())
         worst = max(worst, diff)
         total += diff
         assert diff <= tol, f"{label}: position {pos} (first wrong of the request): |diff| {diff:.3e} > {tol:.3e}"
-    if dtype == "bfloat16" and got_rows:
-        mean = total / len(got_rows)
-        assert mean <= BF16_MEAN_TOL * top, f"{label}: mean |diff| over the positions {mean:.3e} > {BF16_MEAN_TOL * top:.3e}"
+    if dtype == "bfloat16" and len(got_rows) >= 16:
+        mean, most = total / len(got_rows), BF16_MEAN_FLOORS * float(floor.mean())
+        assert mean <= most, f"{label}: mean |diff| over the positions {mean:.3e} > {most:.3e}"
     return worst
 
 

@@ -229,6 +229,16 @@ def test_random_model_of_the_design_runs(folders):
     assert torch.isfinite(lg).all()
 
 
+
+def _close(got, want, dtype, label=""):
+    """A kernel that computes in float and rounds once at the store: within float noise on the 32-bit path, within
+    one rounding of the value itself (2^-8 of its size) on the 16-bit path."""
+    got, want = got.double(), want.double()
+    allowed = 1e-5 * (1.0 + want.abs()) if dtype == "float32" else 2.0 ** -8 * 1.01 * want.abs() + 1e-3
+    bad = (got - want).abs() > allowed
+    assert not bool(bad.any()), f"{label}: {int(bad.sum())} entries off, the worst by {float(((got - want).abs() - allowed).max()):.3e}"
+
+
 # ---- kernels alone, with inputs made so that a fault shows ---------------------------------------------------
 def _chunk_attention(dtype, nh, nkvh, dk, dv, chunk, lens_before, lens_new, q_of, kernel="general", splits=1, seed=0,
                      sinks=True, turn=True):
@@ -389,9 +399,8 @@ def test_pair_sum_and_two_norms_in_one_kernel(dtype, d):
              d + 8, lib.ptr(cw2), lib.ptr(y2), d, 1e-5, 7, d)
     v = x0.double() + (d1.double() + d2.double())
     assert float((x.cpu().double() - v).abs().max()) < 1e-5
-    tol = 1e-5 if dtype == "float32" else 2e-2
-    assert float((y1[:, :d].cpu().double() - DP.rms_norm(v, w1.double(), 1e-5)).abs().max()) < tol
-    assert float((y2.cpu().double() - DP.rms_norm(v, w2.double(), 1e-5)).abs().max()) < tol
+    _close(y1[:, :d].cpu(), DP.rms_norm(v, w1.double(), 1e-5), dtype, "first norm")
+    _close(y2.cpu(), DP.rms_norm(v, w2.double(), 1e-5), dtype, "second norm")
     assert float(y1[:, d:].abs().max()) == 0.0
     # gathered rows, one output, no weight: the sum itself, the stream untouched
     rows = torch.tensor([5, 0], dtype=torch.int32, device="cuda")
@@ -400,7 +409,7 @@ def test_pair_sum_and_two_norms_in_one_kernel(dtype, d):
              0.0, 2, d)
     assert torch.equal(x, before)
     want = (before.cpu().double() + d1.double())[[5, 0]]
-    assert float((y2[:2].cpu().double() - want).abs().max()) < tol
+    _close(y2[:2].cpu(), want, dtype, "gathered rows")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -444,24 +453,24 @@ def test_causal_convolution_across_steps_in_a_used_slot(dtype, taps, residual):
             at[i] += sizes[i]
     for i, s in enumerate(seqs):
         want = DP.causal_conv(s.double(), w.double()) + (s.double() if residual else 0)
-        tol = 1e-5 if dtype == "float32" else 3e-2
-        assert float((got[i].double() - want).abs().max()) < tol, f"sequence {i}"
+        _close(got[i], want, dtype, f"sequence {i}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nh, nkvh, dk, dv, rdims, taps", [(4, 2, 16, 24, 8, 3), (3, 3, 10, 6, 10, 2), (2, 1, 64, 32, 0, 1),
-                                                          (6, 2, 48, 48, 48, 4)])
+@pytest.mark.parametrize("nh, nkvh, dk, dv, rdims, taps", [(4, 2, 16, 24, 8, 3), (3, 3, 10, 6, 10, 2), (2, 1, 64, 32, 0, 0),
+                                                          (6, 2, 48, 48, 48, 4), (2, 2, 24, 20, 12, 1),
+                                                          (5, 1, 256, 130, 64, 5)])
 def test_convolution_head_norms_rotations_and_cache_write(dtype, nh, nkvh, dk, dv, rdims, taps):
     """The kernel between the q-k-v product and the attention, in two steps of one sequence (the second continues from
     the state the first left) and with a second sequence beside it: queries out, keys and values in the page and row
-    of their position."""
+    of their position.  ``taps`` 0: no convolution; 1: a weight per channel."""
     from transformer_b200.csrc import lib
     td = torch.float32 if dtype == "float32" else torch.bfloat16
     g = torch.Generator().manual_seed(nh * 100 + dk)
     C = (nh + nkvh) * dk + nkvh * dv
     n_a, n_b = 70, 5
     za, zb = torch.randn(n_a, C, generator=g).to(td), torch.randn(n_b, C, generator=g).to(td)
-    conv = torch.randn(C, taps, generator=g) * 0.5
+    conv = torch.randn(C, max(taps, 1), generator=g) * 0.5
     wq, wk = torch.rand(dk, generator=g) + 0.5, torch.rand(dk, generator=g) + 0.5
     temp = torch.rand(nh, generator=g) + 0.5
     rp = max(rdims // 2, 1)
@@ -489,10 +498,10 @@ def test_convolution_head_norms_rotations_and_cache_write(dtype, nh, nkvh, dk, d
         tok_pos = list(range(lo, hi)) + (list(range(n_b)) if with_b else [])
         starts = [0, hi - lo] + ([hi - lo + n_b] if with_b else [])
         d_seq, d_pos, d_start, d_slots = I(tok_seq), I(tok_pos), I(starts), I([2, 1][:len(lens)])
-        lib.call("tb_head_prep_" + lib.suffix(td), lib.ptr(dz), C, lib.ptr(d_conv) if taps > 1 else 0, lib.ptr(state),
+        lib.call("tb_head_prep_" + lib.suffix(td), lib.ptr(dz), C, lib.ptr(d_conv) if taps else 0, lib.ptr(state),
                  state.stride(0), lib.ptr(d_wq), lib.ptr(d_wk), lib.ptr(d_temp), 1e-5, lib.ptr(d_cos), lib.ptr(d_sin),
                  lib.ptr(d_vcos), lib.ptr(d_vsin), lib.ptr(q), lib.ptr(kc), lib.ptr(vc), lib.ptr(d_seq), lib.ptr(d_pos),
-                 lib.ptr(d_start), lib.ptr(d_slots), lib.ptr(d_table), 2, nt, nh, nkvh, dk, dv, rdims, taps, 0)
+                 lib.ptr(d_start), lib.ptr(d_slots), lib.ptr(d_table), 2, nt, nh, nkvh, dk, dv, rdims, max(taps, 1), 0)
         if taps > 1:
             lib.call("tb_conv_roll_" + lib.suffix(td), lib.ptr(dz), C, lib.ptr(state), state.stride(0), lib.ptr(d_start),
                      lib.ptr(d_slots), len(lens), C, taps)
@@ -500,7 +509,7 @@ def test_convolution_head_norms_rotations_and_cache_write(dtype, nh, nkvh, dk, d
         qs.append(q.cpu())
     tol = 1e-5 if dtype == "float32" else 3e-2
     for z, n, row, got_q in ((za, n_a, 0, torch.cat([qs[0][:66], qs[1]])), (zb, n_b, 1, qs[0][66:])):
-        u = DP.causal_conv(z.double(), conv.double()) if taps > 1 else z.double()
+        u = DP.causal_conv(z.double(), conv.double()) if taps else z.double()
         pos = torch.arange(n)
         nq, nk = nh * dk, nkvh * dk
         q = DP.rms_norm(u[:, :nq].view(n, nh, dk), wq.double(), 1e-5) * temp.double()[None, :, None]

@@ -40,7 +40,7 @@ def build_spec(m: DumalixMeta) -> ModelSpec:
                            ramp=ramp) if x.rot_dims else None
         if isinstance(x, ChunkAttentionMeta):
             mixer = PartSpec.of("attention", width=m.width, nh=x.heads, nkvh=x.kv_heads, dh=x.dim, dv=x.vdim,
-                                scale=x.scale, qk_norm="head", eps=m.eps, conv_taps=x.conv if x.conv > 1 else 0,
+                                scale=x.scale, qk_norm="head", eps=m.eps, conv_taps=x.conv,
                                 temperature=True, sink=True, value_rotation=True, chunk=x.chunk,
                                 position=rope if rope is not None else
                                 PartSpec.of("rope", dh=0, theta=x.rot_base, pairing="adjacent", positions=m.max_context))
@@ -92,7 +92,7 @@ def tensor_plan(m: DumalixMeta) -> List[TensorRule]:
             hq, hk, hv, ho = x.heads * x.dim, x.kv_heads * x.dim, x.kv_heads * x.vdim, x.heads * x.vdim
             rules.append(TensorRule(mx + ("wqkv",), (hq + hk + hv, d), "matrix", (
                 Source((p + "mix.q", p + "mix.k", p + "mix.v"), ((hq, d), (hk, d), (hv, d)), "cat0"),)))
-            if x.conv > 1:
+            if x.conv:
                 T = x.conv
                 rules.append(TensorRule(mx + ("conv",), (hq + hk + hv, T), "norm", (
                     Source((p + "mix.q.conv", p + "mix.k.conv", p + "mix.v.conv"), ((hq, T), (hk, T), (hv, T)), "cat0"),)))

@@ -10,7 +10,8 @@ from it:
                                       rot: {base, dims, scaling: {factor, original, fast, slow}}}
       type "latent_attention": mixer {heads, dim, rot_dim, vdim, kv_rank, scale,
                                       rot: {base, dims, scaling: {factor, original, fast, slow}}}
-      (mask absent: plain causal; rot.scaling absent: none; conv absent or 1: no convolution on the projections;
+      (mask absent: plain causal; rot.scaling absent: none; conv absent: no convolution on the projections, 1: one tap,
+       a weight per channel;
        canon absent: no convolution on what the mixers read)
     max_context (optional): the longest sequence, default 32768.
 """
@@ -63,7 +64,7 @@ class ChunkAttentionMeta:
     dim: int
     vdim: int
     scale: float
-    conv: int               # taps of the convolutions on q, k, v; 1: none
+    conv: int               # taps of the convolutions on q, k, v; 0: none
     chunk: int              # 0: plain causal
     rot_base: float
     rot_dims: int
@@ -77,13 +78,15 @@ class ChunkAttentionMeta:
             raise ConfigError(f"{where}.mask must be an object")
         heads, dim = _num(m, "heads", where), _num(m, "dim", where)
         m = dict(m, kv_heads=m.get("kv_heads", heads), vdim=m.get("vdim", dim), scale=m.get("scale", dim ** -0.5),
-                 conv=m.get("conv", 1))
+                 conv=m.get("conv", 0))
         return cls(heads, _num(m, "kv_heads", where), dim, _num(m, "vdim", where), _num(m, "scale", where, float),
                    _num(m, "conv", where), 0 if mask is None else _num(mask, "size", where + ".mask"), base, dims, ramp)
 
     def to_dict(self):
         out = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale,
-               "conv": self.conv, "rot": _rot_dict(self.rot_base, self.rot_dims, self.rot_ramp)}
+               "rot": _rot_dict(self.rot_base, self.rot_dims, self.rot_ramp)}
+        if self.conv:
+            out["conv"] = self.conv
         if self.chunk:
             out["mask"] = {"size": self.chunk}
         return out
@@ -237,8 +240,8 @@ class DumalixMeta:
                     raise ConfigError(f"{where}.rot.dims must be even and at most dim ({m.rot_dims}, {m.dim})")
                 if m.vdim % 2:
                     raise ConfigError(f"{where}.vdim must be even (the values rotate in pairs), got {m.vdim}")
-                if m.conv < 1 or m.conv > 16 or m.chunk < 0:
-                    raise ConfigError(f"{where}: conv must lie in 1..16, mask.size must not be negative")
+                if m.conv < 0 or m.conv > 16 or m.chunk < 0:
+                    raise ConfigError(f"{where}: conv must lie in 0..16, mask.size must not be negative")
             else:
                 if m.rot_dims < 0 or m.rot_dims > m.rot_dim or m.rot_dims % 2:
                     raise ConfigError(f"{where}.rot.dims must be even and at most rot_dim ({m.rot_dims}, {m.rot_dim})")

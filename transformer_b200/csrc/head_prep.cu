@@ -8,10 +8,18 @@
 //   queries go to `qout`, keys and values into the paged cache
 //
 // The convolution, the norm, the temperature and the rotations are optional (taps = 1, null weights, null tables).
-// Everything is float; one rounding at each store.  One block per token: the convolved row waits in shared memory,
-// then a warp takes a head at a time.  In a step of one token per sequence the block also moves the convolution's
-// state on; after any other step tb_causal_conv's roll kernel does.
+// Everything is float; one rounding at each store.
+//
+// A warp takes ONE head (a query, key or value head) of a tile of consecutive tokens; a lane holds the pairs
+// (2i, 2i + 1), i = lane, lane + 32, ..., of that head in registers from the convolution to the store, so nothing
+// waits on another warp.  A block is four heads; the convolution's weights of a head wait in shared memory, taps
+// major, so that a tile of tokens reads them from there (when they fit).  The host picks the tile: one token when a
+// step has few (decoding: every (token, head) its own warp), eight in a prompt.  In a step of one token per
+// sequence the warp also moves the convolution's state on; after any other step tb_conv_roll does.
 #include "common.cuh"
+
+constexpr int HP_WARPS = 4;
+constexpr int HP_PAIRS = 4;      // pairs per lane: heads of up to 256 entries
 
 struct HeadPrepArgs {
     const void* z;          // [nt, ldz]  q | k | v as the product left them
@@ -33,94 +41,154 @@ struct HeadPrepArgs {
     const int* seq_start;
     const int* slots;
     const int* page_table;
-    int max_pages, ldz, nh, nkvh, dk, dv, rdims, taps, decode;
+    int max_pages, ldz, nt, nh, nkvh, dk, dv, rdims, taps, decode, tok_tile, staged;
     float eps;
 };
 
-template <typename T>
-__global__ void __launch_bounds__(128) head_prep_kernel(const HeadPrepArgs a) {
-    pdl_sync();
-    extern __shared__ __align__(16) float u_s[];
-    const int t = blockIdx.x;
-    const int C = (a.nh + a.nkvh) * a.dk + a.nkvh * a.dv;
-    const int b = a.tok_seq[t], pos = a.tok_pos[t];
-    const int tl = t - a.seq_start[b];
-    const T* z = static_cast<const T*>(a.z);
-    float* st = a.state ? a.state + (size_t)a.slots[b] * a.state_pitch : nullptr;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        const float own = ldf(z + (size_t)t * a.ldz + c);
-        float acc = own;
-        if (a.conv) {
-            acc = 0.f;
-            for (int j = 0; j < a.taps; ++j) {
-                const int back = a.taps - 1 - j;
-                float v;
-                if (back == 0) v = own;
-                else if (tl - back >= 0) v = ldf(z + (size_t)(t - back) * a.ldz + c);
-                else v = st[(size_t)(a.taps - 1 + tl - back) * C + c];
-                acc += a.conv[(size_t)c * a.taps + j] * v;
-            }
-            if (a.decode) {
-                for (int i = 0; i + 2 < a.taps; ++i) st[(size_t)i * C + c] = st[(size_t)(i + 1) * C + c];
-                if (a.taps > 1) st[(size_t)(a.taps - 2) * C + c] = own;
-            }
-        }
-        u_s[c] = acc;
-    }
-    __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    const int page = a.page_table[(size_t)b * a.max_pages + pos / TB_PAGE];
-    const int prow = pos % TB_PAGE;
-    const int heads = a.nh + 2 * a.nkvh;
-    const int half = a.rdims / 2;
-    for (int h = warp; h < heads; h += nw) {
-        if (h < a.nh + a.nkvh) {
-            const bool is_q = h < a.nh;
-            const float* src = u_s + (size_t)h * a.dk;
-            const float* w = is_q ? a.wq : a.wk;
-            float rs = 1.f;
-            if (w) {
-                float ss = 0.f;
-                for (int c = lane; c < a.dk; c += 32) ss += src[c] * src[c];
-                rs = 1.0f / sqrtf(warp_sum(ss) / (float)a.dk + a.eps);
-            }
-            if (is_q && a.temp) rs *= a.temp[h];
-            T* dst;
-            if (is_q) dst = static_cast<T*>(a.qout) + ((size_t)t * a.nh + h) * a.dk;
-            else if (a.kc) dst = static_cast<T*>(a.kc) + (((size_t)page * a.nkvh + (h - a.nh)) * TB_PAGE + prow) * a.dk;
-            else continue;
-            for (int i = lane; 2 * i < a.dk; i += 32) {
-                float x0 = src[2 * i] * rs, x1 = 2 * i + 1 < a.dk ? src[2 * i + 1] * rs : 0.f;
-                if (w) {
-                    x0 *= w[2 * i];
-                    if (2 * i + 1 < a.dk) x1 *= w[2 * i + 1];
-                }
-                if (i < half) {
-                    const float co = a.cosT[(size_t)pos * half + i], si = a.sinT[(size_t)pos * half + i];
-                    const float r0 = x0 * co - x1 * si, r1 = x1 * co + x0 * si;
-                    x0 = r0;
-                    x1 = r1;
-                }
-                stf(dst + 2 * i, x0);
-                if (2 * i + 1 < a.dk) stf(dst + 2 * i + 1, x1);
-            }
+// two neighbouring entries, as one access where the layout allows it
+template <typename T, bool VEC>
+__device__ __forceinline__ void ld2(const T* p, bool two, float& x0, float& x1) {
+    if constexpr (VEC) {
+        if constexpr (sizeof(T) == 2) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+            x0 = f.x;
+            x1 = f.y;
         } else {
-            if (!a.vc) continue;
-            const int g = h - a.nh - a.nkvh;
-            const float* src = u_s + (size_t)(a.nh + a.nkvh) * a.dk + (size_t)g * a.dv;
-            T* dst = static_cast<T*>(a.vc) + (((size_t)page * a.nkvh + g) * TB_PAGE + prow) * a.dv;
-            const int vhalf = a.dv / 2;
-            for (int i = lane; 2 * i < a.dv; i += 32) {
-                float x0 = src[2 * i], x1 = 2 * i + 1 < a.dv ? src[2 * i + 1] : 0.f;
-                if (a.vcos && i < vhalf) {
-                    const float co = a.vcos[(size_t)pos * vhalf + i], si = a.vsin[(size_t)pos * vhalf + i];
-                    const float r0 = x0 * co - x1 * si, r1 = x1 * co + x0 * si;
-                    x0 = r0;
-                    x1 = r1;
+            const float2 f = *reinterpret_cast<const float2*>(p);
+            x0 = f.x;
+            x1 = f.y;
+        }
+    } else {
+        x0 = ldf(p);
+        x1 = two ? ldf(p + 1) : 0.f;
+    }
+}
+template <typename T, bool VEC>
+__device__ __forceinline__ void st2(T* p, bool two, float x0, float x1) {
+    if constexpr (VEC) {
+        if constexpr (sizeof(T) == 2) *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(x0, x1);
+        else *reinterpret_cast<float2*>(p) = make_float2(x0, x1);
+    } else {
+        stf(p, x0);
+        if (two) stf(p + 1, x1);
+    }
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(HP_WARPS * 32) head_prep_kernel(const HeadPrepArgs a) {
+    pdl_sync();
+    extern __shared__ __align__(16) float w_s[];       // [HP_WARPS][taps][dmax] when staged
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int h = blockIdx.y * HP_WARPS + warp;
+    if (h >= a.nh + 2 * a.nkvh) return;
+    const int C = (a.nh + a.nkvh) * a.dk + a.nkvh * a.dv;
+    const int kind = h < a.nh ? 0 : h < a.nh + a.nkvh ? 1 : 2;             // query, key, value
+    const int dim = kind == 2 ? a.dv : a.dk;
+    const int coff = kind == 2 ? (a.nh + a.nkvh) * a.dk + (h - a.nh - a.nkvh) * a.dv : h * a.dk;
+    if ((kind == 1 && !a.kc) || (kind == 2 && !a.vc)) {
+        if (!(a.decode && a.conv && a.taps > 1)) return;                   // nothing to write, no state to move on
+    }
+    const int dmax = a.dk > a.dv ? a.dk : a.dv;
+    const bool conv = a.conv != nullptr;        // one tap: a weight per channel, no state
+    float* ws = w_s + (size_t)warp * a.taps * dmax;
+    if (conv && a.staged) {
+        for (int e = lane; e < dim * a.taps; e += 32) {
+            const int c = e / a.taps, j = e - c * a.taps;
+            ws[j * dmax + c] = a.conv[(size_t)(coff + c) * a.taps + j];
+        }
+        __syncwarp();
+    }
+    const T* z = static_cast<const T*>(a.z);
+    const float* w = kind == 0 ? a.wq : kind == 1 ? a.wk : nullptr;
+    const int half = kind == 2 ? (a.vcos ? a.dv / 2 : 0) : a.rdims / 2;
+    const float* cosT = kind == 2 ? a.vcos : a.cosT;
+    const float* sinT = kind == 2 ? a.vsin : a.sinT;
+    const int t_end = min(a.nt, (int)(blockIdx.x + 1) * a.tok_tile);
+    for (int t = blockIdx.x * a.tok_tile; t < t_end; ++t) {
+        const int b = a.tok_seq[t], pos = a.tok_pos[t];
+        const int tl = t - a.seq_start[b];
+        float* st = a.state ? a.state + (size_t)a.slots[b] * a.state_pitch : nullptr;
+        float x0[HP_PAIRS], x1[HP_PAIRS];
+        float ss = 0.f;
+#pragma unroll
+        for (int r = 0; r < HP_PAIRS; ++r) {
+            const int i = lane + 32 * r;
+            x0[r] = x1[r] = 0.f;
+            if (2 * i >= dim) continue;
+            const bool two = 2 * i + 1 < dim;
+            const int c = coff + 2 * i;
+            float o0, o1;
+            ld2<T, VEC>(z + (size_t)t * a.ldz + c, two, o0, o1);
+            float a0 = o0, a1 = o1;
+            if (conv) {
+                a0 = a1 = 0.f;
+                for (int j = 0; j < a.taps; ++j) {
+                    const int back = a.taps - 1 - j;
+                    float v0, v1;
+                    if (back == 0) {
+                        v0 = o0;
+                        v1 = o1;
+                    } else if (tl - back >= 0) {
+                        ld2<T, VEC>(z + (size_t)(t - back) * a.ldz + c, two, v0, v1);
+                    } else {
+                        const float* sp = st + (size_t)(a.taps - 1 + tl - back) * C + c;
+                        v0 = sp[0];
+                        v1 = two ? sp[1] : 0.f;
+                    }
+                    float w0, w1;
+                    if (a.staged) {
+                        w0 = ws[j * dmax + 2 * i];
+                        w1 = two ? ws[j * dmax + 2 * i + 1] : 0.f;
+                    } else {
+                        w0 = a.conv[(size_t)c * a.taps + j];
+                        w1 = two ? a.conv[(size_t)(c + 1) * a.taps + j] : 0.f;
+                    }
+                    a0 += w0 * v0;
+                    a1 += w1 * v1;
                 }
-                stf(dst + 2 * i, x0);
-                if (2 * i + 1 < a.dv) stf(dst + 2 * i + 1, x1);
+                if (a.decode && a.taps > 1) {      // one token of this sequence in the step: its state moves on by one input
+                    for (int k = 0; k + 2 < a.taps; ++k) {
+                        st[(size_t)k * C + c] = st[(size_t)(k + 1) * C + c];
+                        if (two) st[(size_t)k * C + c + 1] = st[(size_t)(k + 1) * C + c + 1];
+                    }
+                    st[(size_t)(a.taps - 2) * C + c] = o0;
+                    if (two) st[(size_t)(a.taps - 2) * C + c + 1] = o1;
+                }
             }
+            x0[r] = a0;
+            x1[r] = a1;
+            ss += a0 * a0 + a1 * a1;
+        }
+        T* dst;
+        if (kind == 0) {
+            dst = static_cast<T*>(a.qout) + ((size_t)t * a.nh + h) * a.dk;
+        } else {
+            T* base = static_cast<T*>(kind == 1 ? a.kc : a.vc);
+            if (!base) continue;
+            const int page = a.page_table[(size_t)b * a.max_pages + pos / TB_PAGE];
+            const int g = kind == 1 ? h - a.nh : h - a.nh - a.nkvh;
+            dst = base + (((size_t)page * a.nkvh + g) * TB_PAGE + pos % TB_PAGE) * dim;
+        }
+        float rs = 1.f;
+        if (w) rs = 1.0f / sqrtf(warp_sum(ss) / (float)dim + a.eps);
+        if (kind == 0 && a.temp) rs *= a.temp[h];
+#pragma unroll
+        for (int r = 0; r < HP_PAIRS; ++r) {
+            const int i = lane + 32 * r;
+            if (2 * i >= dim) continue;
+            const bool two = 2 * i + 1 < dim;
+            float y0 = x0[r] * rs, y1 = x1[r] * rs;
+            if (w) {
+                y0 *= w[2 * i];
+                if (two) y1 *= w[2 * i + 1];
+            }
+            if (i < half) {
+                const float co = cosT[(size_t)pos * half + i], si = sinT[(size_t)pos * half + i];
+                const float r0 = y0 * co - y1 * si, r1 = y1 * co + y0 * si;
+                y0 = r0;
+                y1 = r1;
+            }
+            st2<T, VEC>(dst + 2 * i, two, y0, y1);
         }
     }
 }
@@ -139,12 +207,24 @@ extern "C" {
         if (vcos && (dv % 2 || !vsin)) return TB_ERR_ARG;                                                             \
         const long long C = (long long)(nh + nkvh) * dk + (long long)nkvh * dv;                                       \
         if (ldz < C || (conv && taps > 1 && state_pitch < (taps - 1) * C)) return TB_ERR_ARG;                         \
-        if (C * 4 > 48 * 1024) return TB_ERR_UNSUPPORTED;                                                             \
+        if (dk > 64 * HP_PAIRS || dv > 64 * HP_PAIRS) return TB_ERR_UNSUPPORTED;                                      \
         if (nt == 0) return 0;                                                                                        \
+        const int heads = nh + 2 * nkvh, groups = (heads + HP_WARPS - 1) / HP_WARPS;                                  \
+        /* a tile of eight tokens once that still leaves a few hundred blocks; else one token a warp */             \
+        const int tile = (long long)nt * groups >= 2048 ? 8 : 1;                                           \
+        size_t smem = conv ? (size_t)HP_WARPS * taps * (dk > dv ? dk : dv) * 4 : 0;                       \
+        const int staged = smem > 0 && smem <= 48 * 1024 && tile > 1;                                                 \
+        if (!staged) smem = 0;                                                                                        \
         HeadPrepArgs a{z, conv, state, state_pitch, wq, wk, temp, cosT, sinT, vcos, vsin, qout, kc, vc, tok_seq,      \
-                       tok_pos, seq_start, slots, page_table, max_pages, ldz, nh, nkvh, dk, dv, rdims, taps,          \
-                       decode ? 1 : 0, eps};                                                                          \
-        TB_LAUNCH((head_prep_kernel<T>), nt, 128, (size_t)C * 4, s, a);                                               \
+                       tok_pos, seq_start, slots, page_table, max_pages, ldz, nt, nh, nkvh, dk, dv, rdims, taps,      \
+                       decode ? 1 : 0, tile, staged, eps};                                                            \
+        const size_t es = sizeof(T);                                                                                  \
+        const bool vec = dk % 2 == 0 && dv % 2 == 0 && ldz % 2 == 0 && (uintptr_t)z % (2 * es) == 0 &&                \
+                         (uintptr_t)qout % (2 * es) == 0 && (uintptr_t)kc % (2 * es) == 0 &&                          \
+                         (uintptr_t)vc % (2 * es) == 0;                                                               \
+        const dim3 grid((nt + tile - 1) / tile, groups);                                                              \
+        if (vec) TB_LAUNCH((head_prep_kernel<T, true>), grid, HP_WARPS * 32, smem, s, a);                             \
+        else TB_LAUNCH((head_prep_kernel<T, false>), grid, HP_WARPS * 32, smem, s, a);                                \
         return tb_last_error();                                                                                       \
     }
 TB_HEAD_PREP(f32, float)

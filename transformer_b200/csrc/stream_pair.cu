@@ -44,35 +44,82 @@ pair_add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ d1, const T
 // ---- causal convolution over time ------------------------------------------------------------------------
 // y[t, c] = (residual ? u[t, c] : 0) + sum_j w[c, j] * u[t - taps + 1 + j, c]; the inputs before a step's first
 // token come from the sequence's state, [taps - 1, C] floats, oldest first (zeros when the sequence starts).
-// One thread per (token, channel).  In a step of one token per sequence (`roll`) the same thread also moves the
-// state on; after any other step conv_roll_kernel does, once every token has read the old one.
-template <typename T>
-__global__ void __launch_bounds__(256)
+// One thread per (token, V neighbouring channels): V entries of 16 bytes together where the layout allows it, else
+// one.  In a step of one token per sequence (`roll`) the same thread also moves the state on; after any other step
+// conv_roll_kernel does, once every token has read the old one.
+template <typename T, int V>
+struct ConvVec {
+    float v[V];
+    __device__ __forceinline__ void load(const T* p) {
+        if constexpr (V == 1) {
+            v[0] = ldf(p);
+        } else if constexpr (sizeof(T) == 2) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(p);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int i = 0; i < V / 2; ++i) {
+                const float2 f = __bfloat1622float2(h[i]);
+                v[2 * i] = f.x;
+                v[2 * i + 1] = f.y;
+            }
+        } else {
+            const float4 f = *reinterpret_cast<const float4*>(p);
+            v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+        }
+    }
+    __device__ __forceinline__ void store(T* p) const {
+        if constexpr (V == 1) {
+            stf(p, v[0]);
+        } else if constexpr (sizeof(T) == 2) {
+            uint4 raw;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int i = 0; i < V / 2; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            *reinterpret_cast<uint4*>(p) = raw;
+        } else {
+            *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+        }
+    }
+};
+
+template <typename T, int V>
+__global__ void __launch_bounds__(128)
 causal_conv_kernel(const T* __restrict__ u, int ldu, const float* __restrict__ w, float* __restrict__ state,
                    long long state_pitch, T* __restrict__ y, int ldy, const int* __restrict__ tok_seq,
                    const int* __restrict__ seq_start, const int* __restrict__ slots, int nt, int C, int taps,
                    int residual, int roll) {
     pdl_sync();
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (long long)nt * C) return;
-    const int t = (int)(idx / C), c = (int)(idx - (long long)t * C);
+    const int t = blockIdx.x;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+    if (c >= C) return;
     const int b = tok_seq[t];
     const int tl = t - seq_start[b];
-    float* st = state + (size_t)slots[b] * state_pitch;
-    const float own = ldf(u + (size_t)t * ldu + c);
-    float acc = residual ? own : 0.f;
+    float* st = state ? state + (size_t)slots[b] * state_pitch : nullptr;
+    ConvVec<T, V> own, in, acc;
+    own.load(u + (size_t)t * ldu + c);
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc.v[i] = residual ? own.v[i] : 0.f;
     for (int j = 0; j < taps; ++j) {
         const int back = taps - 1 - j;                 // this tap reads the input `back` tokens earlier
-        float v;
-        if (back == 0) v = own;
-        else if (tl - back >= 0) v = ldf(u + (size_t)(t - back) * ldu + c);
-        else v = st[(size_t)(taps - 1 + tl - back) * C + c];
-        acc += w[(size_t)c * taps + j] * v;
+        if (back == 0) {
+            in = own;
+        } else if (tl - back >= 0) {
+            in.load(u + (size_t)(t - back) * ldu + c);
+        } else {
+            const float* sp = st + (size_t)(taps - 1 + tl - back) * C + c;
+#pragma unroll
+            for (int i = 0; i < V; ++i) in.v[i] = sp[i];
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc.v[i] += w[(size_t)(c + i) * taps + j] * in.v[i];
     }
-    stf(y + (size_t)t * ldy + c, acc);
-    if (roll) {            // tl == 0: the state moves on by one input
-        for (int i = 0; i + 2 < taps; ++i) st[(size_t)i * C + c] = st[(size_t)(i + 1) * C + c];
-        if (taps > 1) st[(size_t)(taps - 2) * C + c] = own;
+    acc.store(y + (size_t)t * ldy + c);
+    if (roll && taps > 1) {            // tl == 0: the state moves on by one input
+        for (int k = 0; k + 2 < taps; ++k)
+#pragma unroll
+            for (int i = 0; i < V; ++i) st[(size_t)k * C + c + i] = st[(size_t)(k + 1) * C + c + i];
+#pragma unroll
+        for (int i = 0; i < V; ++i) st[(size_t)(taps - 2) * C + c + i] = own.v[i];
     }
 }
 
@@ -116,9 +163,17 @@ extern "C" {
         if (nt < 0 || B <= 0 || C <= 0 || taps < 1 || taps > 16 || ldu < C || ldy < C) return TB_ERR_ARG;             \
         if (taps > 1 && (!state || state_pitch < (long long)(taps - 1) * C)) return TB_ERR_ARG;                       \
         if (nt == 0) return 0;                                                                                        \
-        const long long n = (long long)nt * C;                                                                        \
-        TB_LAUNCH((causal_conv_kernel<T>), (unsigned)((n + 255) / 256), 256, 0, s, (const T*)u, ldu, w, state,        \
-                  state_pitch, (T*)y, ldy, tok_seq, seq_start, slots, nt, C, taps, residual, decode ? 1 : 0);         \
+        constexpr int V = 16 / sizeof(T);                                                                             \
+        const bool vec = C % V == 0 && ldu % V == 0 && ldy % V == 0 && (uintptr_t)u % 16 == 0 && (uintptr_t)y % 16 == 0; \
+        if (vec) {                                                                                                    \
+            const dim3 grid(nt, (C / V + 127) / 128);                                                                 \
+            TB_LAUNCH((causal_conv_kernel<T, V>), grid, 128, 0, s, (const T*)u, ldu, w, state, state_pitch, (T*)y,    \
+                      ldy, tok_seq, seq_start, slots, nt, C, taps, residual, decode ? 1 : 0);                         \
+        } else {                                                                                                      \
+            const dim3 grid(nt, (C + 127) / 128);                                                                     \
+            TB_LAUNCH((causal_conv_kernel<T, 1>), grid, 128, 0, s, (const T*)u, ldu, w, state, state_pitch, (T*)y,    \
+                      ldy, tok_seq, seq_start, slots, nt, C, taps, residual, decode ? 1 : 0);                         \
+        }                                                                                                             \
         int rc = tb_last_error();                                                                                     \
         if (rc || decode || taps == 1) return rc;                                                                     \
         TB_LAUNCH((conv_roll_kernel<T>), (unsigned)(((long long)B * C + 255) / 256), 256, 0, s, (const T*)u, ldu,     \

@@ -16,7 +16,7 @@ windowed attention with the gate in its epilogue -> output product  (csrc/attent
 
 A second family, again parameters of the same mixer: a short causal convolution over time on every channel of the
 q, k and v projections, ``conv_taps`` wide (weights ``conv``; the last ``conv_taps - 1`` projected rows are state of
-the sequence); an RMS norm per head with one weight of the head's size shared by all heads (``qk_norm="head"``); a
+the sequence; one tap is a weight per channel); an RMS norm per head with one weight of the head's size shared by all heads (``qk_norm="head"``); a
 learned multiplier of every query head's scores (``temperature``, weights ``temp``); values that are cached rotated
 by their own position over all of their entries, in adjacent pairs, with the rotary part's base and no rescaling,
 and an output that is turned back by the query's position (``value_rotation``); a mask of chunks (``chunk``:
