@@ -413,25 +413,30 @@ def test_pair_sum_and_two_norms_in_one_kernel(dtype, d):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("taps, residual", [(1, 1), (2, 0), (3, 1), (5, 0), (16, 1)])
-def test_causal_convolution_across_steps_in_a_used_slot(dtype, taps, residual):
+@pytest.mark.parametrize("taps, residual", [(1, 1), (2, 0), (3, 1), (4, 1), (5, 0), (16, 1)])
+@pytest.mark.parametrize("C, pad, lens, steps", [
+    (20, 4, (9, 23, 4), ([1, 7, 2], [2, 1, 1], [1, 1, 1], [5, 14, 0])),
+    # channels in groups of 16 bytes and steps of many tokens: the form that slides a window over a tile of tokens,
+    # with portions that start inside a tile, one of them a single token
+    (48, 8, (75, 150, 30), ([3, 70, 2], [2, 1, 1], [1, 1, 1], [69, 78, 26])),
+])
+def test_causal_convolution_across_steps_in_a_used_slot(dtype, taps, residual, C, pad, lens, steps):
     """Three sequences in steps of unequal sizes (down to one token, shorter than the taps' reach) in slots whose
     rows held other sequences' inputs before: the same as the convolution of each whole sequence."""
     from transformer_b200.csrc import lib
     td = torch.float32 if dtype == "float32" else torch.bfloat16
     g = torch.Generator().manual_seed(taps)
-    C, pad = 20, 4
     w = torch.randn(C, taps, generator=g)
-    seqs = [torch.randn(n, C, generator=g).to(td) for n in (9, 23, 4)]
+    seqs = [torch.randn(n, C, generator=g).to(td) for n in lens]
     state = torch.randn(5, max(taps - 1, 1) * C + 3, generator=g).cuda()
     slots = [3, 0, 4]
     for s in slots:
         state[s].zero_()
-    got = [torch.zeros(n, C, dtype=td) for n in (9, 23, 4)]
+    got = [torch.zeros(n, C, dtype=td) for n in lens]
     at = [0, 0, 0]
     I = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
     cw = w.cuda()
-    for sizes in ([1, 7, 2], [2, 1, 1], [1, 1, 1], [5, 14, 0]):
+    for sizes in steps:
         live = [i for i, n in enumerate(sizes) if n]
         u = torch.cat([seqs[i][at[i]:at[i] + sizes[i]] for i in live])
         nt = u.shape[0]
@@ -461,14 +466,16 @@ def test_causal_convolution_across_steps_in_a_used_slot(dtype, taps, residual):
                                                           (6, 2, 48, 48, 48, 4), (2, 2, 24, 20, 12, 1),
                                                           (5, 1, 256, 130, 64, 5)])
 def test_convolution_head_norms_rotations_and_cache_write(dtype, nh, nkvh, dk, dv, rdims, taps):
-    """The kernel between the q-k-v product and the attention, in two steps of one sequence (the second continues from
-    the state the first left) and with a second sequence beside it: queries out, keys and values in the page and row
-    of their position.  ``taps`` 0: no convolution; 1: a weight per channel."""
+    """The kernel between the q-k-v product and the attention, in three steps of one sequence (each continues from
+    the state the one before left: a step shorter than the taps' reach, a step of many tokens, which takes the form
+    that slides over tiles of tokens, and a few more) and with a second sequence beside it that starts inside a tile:
+    queries out, keys and values in the page and row of their position.  ``taps`` 0: no convolution; 1: a weight per
+    channel."""
     from transformer_b200.csrc import lib
     td = torch.float32 if dtype == "float32" else torch.bfloat16
     g = torch.Generator().manual_seed(nh * 100 + dk)
     C = (nh + nkvh) * dk + nkvh * dv
-    n_a, n_b = 70, 5
+    n_a, n_b = 140, 5
     za, zb = torch.randn(n_a, C, generator=g).to(td), torch.randn(n_b, C, generator=g).to(td)
     conv = torch.randn(C, max(taps, 1), generator=g) * 0.5
     wq, wk = torch.rand(dk, generator=g) + 0.5, torch.rand(dk, generator=g) + 0.5
@@ -479,7 +486,7 @@ def test_convolution_head_norms_rotations_and_cache_write(dtype, nh, nkvh, dk, d
     pos_all = torch.arange(200, dtype=torch.float64)[:, None]
     cos, sin = torch.cos(pos_all * f).float() * 1.1, torch.sin(pos_all * f).float() * 1.1
     vcos, vsin = torch.cos(pos_all * fv).float(), torch.sin(pos_all * fv).float()
-    table = torch.tensor([[3, 1], [2, 0]], dtype=torch.int32)
+    table = torch.tensor([[3, 1, 4], [2, 0, 0]], dtype=torch.int32)
     kc = torch.zeros(5, nkvh, 64, dk, dtype=td, device="cuda")
     vc = torch.zeros(5, nkvh, 64, dv, dtype=td, device="cuda")
     state = torch.randn(4, max(taps - 1, 1) * C, generator=g).cuda()
@@ -488,7 +495,7 @@ def test_convolution_head_norms_rotations_and_cache_write(dtype, nh, nkvh, dk, d
     d_conv, d_wq, d_wk, d_temp = conv.cuda(), wq.cuda(), wk.cuda(), temp.cuda()
     d_cos, d_sin, d_vcos, d_vsin, d_table = cos.cuda(), sin.cuda(), vcos.cuda(), vsin.cuda(), table.cuda()
     qs = []
-    for (lo, hi, with_b) in ((0, 66, True), (66, 70, False)):
+    for (lo, hi, with_b) in ((0, 3, False), (3, 133, True), (133, 140, False)):
         z = torch.cat([za[lo:hi]] + ([zb] if with_b else []))
         nt = z.shape[0]
         dz = z.cuda()
@@ -501,14 +508,14 @@ def test_convolution_head_norms_rotations_and_cache_write(dtype, nh, nkvh, dk, d
         lib.call("tb_head_prep_" + lib.suffix(td), lib.ptr(dz), C, lib.ptr(d_conv) if taps else 0, lib.ptr(state),
                  state.stride(0), lib.ptr(d_wq), lib.ptr(d_wk), lib.ptr(d_temp), 1e-5, lib.ptr(d_cos), lib.ptr(d_sin),
                  lib.ptr(d_vcos), lib.ptr(d_vsin), lib.ptr(q), lib.ptr(kc), lib.ptr(vc), lib.ptr(d_seq), lib.ptr(d_pos),
-                 lib.ptr(d_start), lib.ptr(d_slots), lib.ptr(d_table), 2, nt, nh, nkvh, dk, dv, rdims, max(taps, 1), 0)
+                 lib.ptr(d_start), lib.ptr(d_slots), lib.ptr(d_table), 3, nt, nh, nkvh, dk, dv, rdims, max(taps, 1), 0)
         if taps > 1:
             lib.call("tb_conv_roll_" + lib.suffix(td), lib.ptr(dz), C, lib.ptr(state), state.stride(0), lib.ptr(d_start),
                      lib.ptr(d_slots), len(lens), C, taps)
         torch.cuda.synchronize()
         qs.append(q.cpu())
     tol = 1e-5 if dtype == "float32" else 3e-2
-    for z, n, row, got_q in ((za, n_a, 0, torch.cat([qs[0][:66], qs[1]])), (zb, n_b, 1, qs[0][66:])):
+    for z, n, row, got_q in ((za, n_a, 0, torch.cat([qs[0], qs[1][:130], qs[2]])), (zb, n_b, 1, qs[1][130:])):
         u = DP.causal_conv(z.double(), conv.double()) if taps else z.double()
         pos = torch.arange(n)
         nq, nk = nh * dk, nkvh * dk

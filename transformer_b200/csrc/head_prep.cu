@@ -20,6 +20,7 @@
 
 constexpr int HP_WARPS = 4;
 constexpr int HP_PAIRS = 4;      // pairs per lane: heads of up to 256 entries
+constexpr int HP_TILE = 4;       // tokens a warp takes in the form for prompts
 
 struct HeadPrepArgs {
     const void* z;          // [nt, ldz]  q | k | v as the product left them
@@ -193,6 +194,174 @@ __global__ void __launch_bounds__(HP_WARPS * 32) head_prep_kernel(const HeadPrep
     }
 }
 
+// The form for prompts: the same warp per head and tile of tokens, with the taps and the pairs per lane known to the
+// compiler.  The head's convolution weights sit in registers, the tile's rows are all asked for before the first is
+// used, and the last TAPS - 1 inputs slide along in registers, so every projected value is read once.  Where a
+// sequence's portion starts inside the tile the window is filled from that sequence's state.  Needs even head
+// sizes (pairs as one access).  TAPS = 1 with no weights is the plain copy.
+template <typename T, int TAPS, int PAIRS, int TILE>
+__global__ void __launch_bounds__(HP_WARPS * 32, PAIRS <= 2 ? 6 : 3) head_prep_tile_kernel(const HeadPrepArgs a) {
+    pdl_sync();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int h = blockIdx.y * HP_WARPS + warp;
+    if (h >= a.nh + 2 * a.nkvh) return;
+    const int C = (a.nh + a.nkvh) * a.dk + a.nkvh * a.dv;
+    const int kind = h < a.nh ? 0 : h < a.nh + a.nkvh ? 1 : 2;             // query, key, value
+    const int dim = kind == 2 ? a.dv : a.dk;
+    const int coff = kind == 2 ? (a.nh + a.nkvh) * a.dk + (h - a.nh - a.nkvh) * a.dv : h * a.dk;
+    if ((kind == 1 && !a.kc) || (kind == 2 && !a.vc)) return;
+    constexpr int HIST = TAPS > 1 ? TAPS - 1 : 1;
+    float wr[PAIRS][2 * TAPS];                      // wr[r][e * TAPS + j]: entry 2i + e of the head, tap j
+#pragma unroll
+    for (int r = 0; r < PAIRS; ++r) {
+        const int i = lane + 32 * r;
+        if (a.conv && 2 * i < dim) {                  // a pair's 2 TAPS weights lie together: 8 bytes at a time
+            const float2* wp = reinterpret_cast<const float2*>(a.conv + (size_t)(coff + 2 * i) * TAPS);
+#pragma unroll
+            for (int k = 0; k < TAPS; ++k) {
+                const float2 f = __ldg(wp + k);
+                wr[r][2 * k] = f.x;
+                wr[r][2 * k + 1] = f.y;
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 2 * TAPS; ++k) wr[r][k] = (k % TAPS == TAPS - 1) ? 1.f : 0.f;
+        }
+    }
+    const T* z = static_cast<const T*>(a.z);
+    const float* w = kind == 0 ? a.wq : kind == 1 ? a.wk : nullptr;
+    const int half = kind == 2 ? (a.vcos ? a.dv / 2 : 0) : a.rdims / 2;
+    const float* cosT = kind == 2 ? a.vcos : a.cosT;
+    const float* sinT = kind == 2 ? a.vsin : a.sinT;
+    float nw0[PAIRS], nw1[PAIRS];                     // the norm's weights of this lane's entries
+#pragma unroll
+    for (int r = 0; r < PAIRS; ++r) {
+        const int i = lane + 32 * r;
+        nw0[r] = (w && 2 * i < dim) ? w[2 * i] : 1.f;
+        nw1[r] = (w && 2 * i < dim) ? w[2 * i + 1] : 1.f;
+    }
+    const float temp_h = (kind == 0 && a.temp) ? a.temp[h] : 1.f;
+    const int t0 = blockIdx.x * TILE;
+    float2 own[TILE][PAIRS];
+#pragma unroll
+    for (int tt = 0; tt < TILE; ++tt)
+#pragma unroll
+        for (int r = 0; r < PAIRS; ++r) {
+            const int i = lane + 32 * r;
+            own[tt][r] = make_float2(0.f, 0.f);
+            if (t0 + tt < a.nt && 2 * i < dim)
+                ld2<T, true>(z + (size_t)(t0 + tt) * a.ldz + coff + 2 * i, true, own[tt][r].x, own[tt][r].y);
+        }
+    // where each of the tile's tokens stands: lane tt looks it up, every lane asks that lane
+    static_assert(TILE <= 32, "a lane per token of the tile");
+    int my_pos = 0, my_page = 0, my_slot = 0, my_first = 0;
+    if (lane < TILE && t0 + lane < a.nt) {
+        const int b = a.tok_seq[t0 + lane];
+        my_pos = a.tok_pos[t0 + lane];
+        my_first = t0 + lane == a.seq_start[b];
+        my_slot = a.slots ? a.slots[b] : 0;
+        if (kind != 0) my_page = a.page_table[(size_t)b * a.max_pages + my_pos / TB_PAGE];
+    }
+    float2 hist[HIST][PAIRS];                          // hist[k]: the input k + 1 tokens back
+    if constexpr (TAPS > 1) {
+        const int b = a.tok_seq[t0];
+        const int tl = t0 - a.seq_start[b];
+        const float* st = a.state + (size_t)__shfl_sync(0xffffffffu, my_slot, 0) * a.state_pitch;
+#pragma unroll
+        for (int k = 0; k < TAPS - 1; ++k)
+#pragma unroll
+            for (int r = 0; r < PAIRS; ++r) {
+                const int i = lane + 32 * r;
+                hist[k][r] = make_float2(0.f, 0.f);
+                if (2 * i >= dim) continue;
+                const int back = k + 1, c = coff + 2 * i;
+                if (tl - back >= 0) {
+                    ld2<T, true>(z + (size_t)(t0 - back) * a.ldz + c, true, hist[k][r].x, hist[k][r].y);
+                } else {
+                    const float* sp = st + (size_t)(TAPS - 1 + tl - back) * C + c;
+                    hist[k][r] = make_float2(sp[0], sp[1]);
+                }
+            }
+    }
+#pragma unroll
+    for (int tt = 0; tt < TILE; ++tt) {
+        const int t = t0 + tt;
+        if (t >= a.nt) break;
+        const int pos = __shfl_sync(0xffffffffu, my_pos, tt);
+        if constexpr (TAPS > 1) {
+            const int first = __shfl_sync(0xffffffffu, my_first, tt), slot = __shfl_sync(0xffffffffu, my_slot, tt);
+            if (tt > 0 && first) {                      // another sequence's portion starts here
+                const float* st = a.state + (size_t)slot * a.state_pitch;
+#pragma unroll
+                for (int k = 0; k < TAPS - 1; ++k)
+#pragma unroll
+                    for (int r = 0; r < PAIRS; ++r) {
+                        const int i = lane + 32 * r;
+                        if (2 * i >= dim) continue;
+                        const float* sp = st + (size_t)(TAPS - 2 - k) * C + coff + 2 * i;
+                        hist[k][r] = make_float2(sp[0], sp[1]);
+                    }
+            }
+        }
+        float x0[PAIRS], x1[PAIRS];
+        float ss = 0.f;
+#pragma unroll
+        for (int r = 0; r < PAIRS; ++r) {
+            float a0 = wr[r][TAPS - 1] * own[tt][r].x, a1 = wr[r][2 * TAPS - 1] * own[tt][r].y;
+            if constexpr (TAPS > 1) {
+#pragma unroll
+                for (int j = 0; j < TAPS - 1; ++j) {
+                    a0 += wr[r][j] * hist[TAPS - 2 - j][r].x;
+                    a1 += wr[r][TAPS + j] * hist[TAPS - 2 - j][r].y;
+                }
+            }
+            x0[r] = a0;
+            x1[r] = a1;
+            ss += a0 * a0 + a1 * a1;
+        }
+        if constexpr (TAPS > 1) {
+#pragma unroll
+            for (int k = TAPS - 2; k > 0; --k)
+#pragma unroll
+                for (int r = 0; r < PAIRS; ++r) hist[k][r] = hist[k - 1][r];
+#pragma unroll
+            for (int r = 0; r < PAIRS; ++r) hist[0][r] = own[tt][r];
+        }
+        T* dst;
+        if (kind == 0) {
+            dst = static_cast<T*>(a.qout) + ((size_t)t * a.nh + h) * a.dk;
+        } else {
+            const int page = __shfl_sync(0xffffffffu, my_page, tt);
+            const int g = kind == 1 ? h - a.nh : h - a.nh - a.nkvh;
+            dst = static_cast<T*>(kind == 1 ? a.kc : a.vc) + (((size_t)page * a.nkvh + g) * TB_PAGE + pos % TB_PAGE) * dim;
+        }
+        float rs = 1.f;
+        if (w) rs = 1.0f / sqrtf(warp_sum(ss) / (float)dim + a.eps);
+        rs *= temp_h;
+#pragma unroll
+        for (int r = 0; r < PAIRS; ++r) {
+            const int i = lane + 32 * r;
+            if (2 * i >= dim) continue;
+            float y0 = x0[r] * rs * nw0[r], y1 = x1[r] * rs * nw1[r];
+            if (i < half) {
+                const float co = __ldg(cosT + (size_t)pos * half + i), si = __ldg(sinT + (size_t)pos * half + i);
+                const float r0 = y0 * co - y1 * si, r1 = y1 * co + y0 * si;
+                y0 = r0;
+                y1 = r1;
+            }
+            st2<T, true>(dst + 2 * i, true, y0, y1);
+        }
+    }
+}
+
+template <typename T, int TAPS>
+static void head_prep_tile_launch(const HeadPrepArgs& a, dim3 grid, int dmax, cudaStream_t s) {
+    constexpr int TILE = HP_TILE;
+    if (dmax <= 64) TB_LAUNCH((head_prep_tile_kernel<T, TAPS, 1, TILE>), grid, HP_WARPS * 32, 0, s, a);
+    else if (dmax <= 128) TB_LAUNCH((head_prep_tile_kernel<T, TAPS, 2, TILE>), grid, HP_WARPS * 32, 0, s, a);
+    else TB_LAUNCH((head_prep_tile_kernel<T, TAPS, 4, TILE>), grid, HP_WARPS * 32, 0, s, a);
+}
+
 extern "C" {
 #define TB_HEAD_PREP(SFX, T)                                                                                          \
     int tb_head_prep_##SFX(const void* z, int ldz, const float* conv, float* state, long long state_pitch,            \
@@ -210,8 +379,8 @@ extern "C" {
         if (dk > 64 * HP_PAIRS || dv > 64 * HP_PAIRS) return TB_ERR_UNSUPPORTED;                                      \
         if (nt == 0) return 0;                                                                                        \
         const int heads = nh + 2 * nkvh, groups = (heads + HP_WARPS - 1) / HP_WARPS;                                  \
-        /* a tile of eight tokens once that still leaves a few hundred blocks; else one token a warp */             \
-        const int tile = (long long)nt * groups >= 2048 ? 8 : 1;                                           \
+        /* a tile of eight tokens in a step of many; else one token a warp */                                         \
+        const int tile = nt >= 64 ? 8 : 1;                                                                            \
         size_t smem = conv ? (size_t)HP_WARPS * taps * (dk > dv ? dk : dv) * 4 : 0;                       \
         const int staged = smem > 0 && smem <= 48 * 1024 && tile > 1;                                                 \
         if (!staged) smem = 0;                                                                                        \
@@ -222,6 +391,17 @@ extern "C" {
         const bool vec = dk % 2 == 0 && dv % 2 == 0 && ldz % 2 == 0 && (uintptr_t)z % (2 * es) == 0 &&                \
                          (uintptr_t)qout % (2 * es) == 0 && (uintptr_t)kc % (2 * es) == 0 &&                          \
                          (uintptr_t)vc % (2 * es) == 0;                                                               \
+        const int taps_eff = conv ? taps : 1;                                                                         \
+        if (vec && tile == 8 && !decode && taps_eff <= 4 && (uintptr_t)conv % 8 == 0) {                               \
+            const int dmax = dk > dv ? dk : dv;                                                                       \
+            const dim3 grid((nt + HP_TILE - 1) / HP_TILE, groups);                                                    \
+            a.taps = taps_eff;                                                                                        \
+            if (taps_eff == 1) head_prep_tile_launch<T, 1>(a, grid, dmax, s);                                         \
+            else if (taps_eff == 2) head_prep_tile_launch<T, 2>(a, grid, dmax, s);                                    \
+            else if (taps_eff == 3) head_prep_tile_launch<T, 3>(a, grid, dmax, s);                                    \
+            else head_prep_tile_launch<T, 4>(a, grid, dmax, s);                                                       \
+            return tb_last_error();                                                                                   \
+        }                                                                                                             \
         const dim3 grid((nt + tile - 1) / tile, groups);                                                              \
         if (vec) TB_LAUNCH((head_prep_kernel<T, true>), grid, HP_WARPS * 32, smem, s, a);                             \
         else TB_LAUNCH((head_prep_kernel<T, false>), grid, HP_WARPS * 32, smem, s, a);                                \

@@ -123,6 +123,81 @@ causal_conv_kernel(const T* __restrict__ u, int ldu, const float* __restrict__ w
     }
 }
 
+// The same sum for a prompt: a thread takes V neighbouring channels of a tile of consecutive tokens.  Its V x TAPS
+// weights are fetched once (16 bytes at a time) and the last TAPS - 1 inputs slide along in registers, so every
+// input is read once, and the tile's rows are all asked for before the first is used.  Where a sequence's portion
+// starts inside the tile the window is filled from that sequence's state.
+template <typename T, int V, int TAPS, int TILE>
+__global__ void __launch_bounds__(64)
+causal_conv_tile_kernel(const T* __restrict__ u, int ldu, const float* __restrict__ w, const float* __restrict__ state,
+                        long long state_pitch, T* __restrict__ y, int ldy, const int* __restrict__ tok_seq,
+                        const int* __restrict__ seq_start, const int* __restrict__ slots, int nt, int C, int residual) {
+    pdl_sync();
+    const int t0 = blockIdx.x * TILE;
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+    if (c >= C) return;
+    float wr[V * TAPS];                                   // wr[i * TAPS + j]: channel c + i, tap j
+    {
+        const float4* wp = reinterpret_cast<const float4*>(w + (size_t)c * TAPS);
+#pragma unroll
+        for (int k = 0; k < V * TAPS / 4; ++k) {
+            const float4 f = wp[k];
+            wr[4 * k] = f.x; wr[4 * k + 1] = f.y; wr[4 * k + 2] = f.z; wr[4 * k + 3] = f.w;
+        }
+    }
+    uint4 raw[TILE];                                      // the tile's rows as they lie in memory, 16 bytes each
+#pragma unroll
+    for (int tt = 0; tt < TILE; ++tt)
+        if (t0 + tt < nt) raw[tt] = *reinterpret_cast<const uint4*>(u + (size_t)(t0 + tt) * ldu + c);
+    ConvVec<T, V> hist[TAPS - 1];                         // hist[k]: the input k + 1 tokens back
+    {
+        const int b = tok_seq[t0];
+        const int tl = t0 - seq_start[b];
+        const float* st = state + (size_t)slots[b] * state_pitch;
+#pragma unroll
+        for (int k = 0; k < TAPS - 1; ++k) {
+            const int back = k + 1;
+            if (tl - back >= 0) {
+                hist[k].load(u + (size_t)(t0 - back) * ldu + c);
+            } else {
+                const float* sp = st + (size_t)(TAPS - 1 + tl - back) * C + c;
+#pragma unroll
+                for (int i = 0; i < V; ++i) hist[k].v[i] = sp[i];
+            }
+        }
+    }
+#pragma unroll
+    for (int tt = 0; tt < TILE; ++tt) {
+        const int t = t0 + tt;
+        if (t >= nt) break;
+        if (tt > 0) {
+            const int b = tok_seq[t];
+            if (t == seq_start[b]) {                      // another sequence's portion starts here
+                const float* st = state + (size_t)slots[b] * state_pitch;
+#pragma unroll
+                for (int k = 0; k < TAPS - 1; ++k) {
+                    const float* sp = st + (size_t)(TAPS - 2 - k) * C + c;
+#pragma unroll
+                    for (int i = 0; i < V; ++i) hist[k].v[i] = sp[i];
+                }
+            }
+        }
+        ConvVec<T, V> own, acc;
+        own.load(reinterpret_cast<const T*>(&raw[tt]));
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            float a = residual ? own.v[i] : 0.f;
+#pragma unroll
+            for (int j = 0; j < TAPS - 1; ++j) a += wr[i * TAPS + j] * hist[TAPS - 2 - j].v[i];
+            acc.v[i] = a + wr[i * TAPS + TAPS - 1] * own.v[i];
+        }
+        acc.store(y + (size_t)t * ldy + c);
+#pragma unroll
+        for (int k = TAPS - 2; k > 0; --k) hist[k] = hist[k - 1];
+        hist[0] = own;
+    }
+}
+
 // The state after a step of n tokens: entry i is the input at local index n - (taps - 1) + i, which is one of the
 // step's rows or, for a short step, an older entry.  One thread per (sequence, channel), so that what it reads of
 // the old state it reads before it writes.
@@ -165,7 +240,20 @@ extern "C" {
         if (nt == 0) return 0;                                                                                        \
         constexpr int V = 16 / sizeof(T);                                                                             \
         const bool vec = C % V == 0 && ldu % V == 0 && ldy % V == 0 && (uintptr_t)u % 16 == 0 && (uintptr_t)y % 16 == 0; \
-        if (vec) {                                                                                                    \
+        constexpr int TILE = 8;                                                                                       \
+        const bool tiled = vec && !decode && nt >= 8 * TILE && taps >= 2 && taps <= 4 && (uintptr_t)w % 16 == 0;      \
+        if (tiled) {                                                                                                  \
+            const dim3 grid((nt + TILE - 1) / TILE, (C / V + 63) / 64);                                               \
+            if (taps == 2)                                                                                            \
+                TB_LAUNCH((causal_conv_tile_kernel<T, V, 2, TILE>), grid, 64, 0, s, (const T*)u, ldu, w, state,      \
+                          state_pitch, (T*)y, ldy, tok_seq, seq_start, slots, nt, C, residual);                       \
+            else if (taps == 3)                                                                                       \
+                TB_LAUNCH((causal_conv_tile_kernel<T, V, 3, TILE>), grid, 64, 0, s, (const T*)u, ldu, w, state,      \
+                          state_pitch, (T*)y, ldy, tok_seq, seq_start, slots, nt, C, residual);                       \
+            else                                                                                                      \
+                TB_LAUNCH((causal_conv_tile_kernel<T, V, 4, TILE>), grid, 64, 0, s, (const T*)u, ldu, w, state,      \
+                          state_pitch, (T*)y, ldy, tok_seq, seq_start, slots, nt, C, residual);                       \
+        } else if (vec) {                                                                                             \
             const dim3 grid(nt, (C / V + 127) / 128);                                                                 \
             TB_LAUNCH((causal_conv_kernel<T, V>), grid, 128, 0, s, (const T*)u, ldu, w, state, state_pitch, (T*)y,    \
                       ldy, tok_seq, seq_start, slots, nt, C, taps, residual, decode ? 1 : 0);                         \
