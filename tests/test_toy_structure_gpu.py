@@ -3,7 +3,7 @@ and stepped without a change to the library's files:
 
   * a cache kind "window" (a ring of the last W keys and values per slot, no pages) with a windowed attention
     mixer that uses it;
-  * a block arrangement "parallel":  x += mixer(norm(x)) + feed_forward(norm(x))  with one norm;
+  * a block arrangement "one_norm_parallel":  x += mixer(norm(x)) + feed_forward(norm(x))  with one norm;
   * a position encoding that is no rotation: a learned offset per position added to queries and keys (it has a
     parameter of its own, which travels with its mixer);
   * an embedding that adds learned absolute positions to the token rows;
@@ -185,7 +185,7 @@ def toy_spec(c: ToyConfig) -> ModelSpec:
     learned = PartSpec.of("learned_offsets", dh=DH, positions=c.context)
     ff = PartSpec.of("swiglu", width=c.width, di=DI)
     first = LayerSpec(PartSpec.of("attention", width=c.width, nh=NH, nkvh=NKVH, dh=DH, position=learned), ff,
-                      mixer_norm=rms, arrangement="parallel")
+                      mixer_norm=rms, arrangement="one_norm_parallel")
     second = LayerSpec(PartSpec.of("window_attention", width=c.width, nh=2, dh=DH, window=c.window), ff, rms, rms)
     return ModelSpec(width=c.width, vocab=c.vocab, max_context=c.context, layers=(first, second),
                      order=(RunEntry(0), RunEntry(1), RunEntry(1)),      # the windowed layer runs twice: two rings
@@ -197,7 +197,7 @@ def toy_spec(c: ToyConfig) -> ModelSpec:
 def toys():
     CACHE_KINDS.register("window", WindowStorage)
     MIXERS.register("window_attention", WindowAttention)
-    ARRANGEMENTS.register("parallel", ParallelBlock)
+    ARRANGEMENTS.register("one_norm_parallel", ParallelBlock)
     POSITIONS.register("learned_offsets", LearnedOffsets)
     EMBEDDINGS.register("lookup_with_positions", LookupWithPositions)
     HEADS.register("capped_linear", CappedHead)
@@ -205,7 +205,7 @@ def toys():
     yield
     unregister_architecture("toy_structure")
     for reg, kind in ((HEADS, "capped_linear"), (EMBEDDINGS, "lookup_with_positions"), (POSITIONS, "learned_offsets"),
-                      (ARRANGEMENTS, "parallel"), (MIXERS, "window_attention"), (CACHE_KINDS, "window")):
+                      (ARRANGEMENTS, "one_norm_parallel"), (MIXERS, "window_attention"), (CACHE_KINDS, "window")):
         reg.unregister(kind)
 
 
@@ -324,9 +324,9 @@ def test_an_unknown_kind_is_refused_by_name(toys, tmp_path):
             tb.load(folder, dtype="float32", max_tokens=128)
     finally:
         CACHE_KINDS.register("window", WindowStorage)
-    ARRANGEMENTS.unregister("parallel")
+    ARRANGEMENTS.unregister("one_norm_parallel")
     try:
-        with pytest.raises(ValueError, match="unknown block arrangement kind 'parallel'.*pre_norm"):
+        with pytest.raises(ValueError, match="unknown block arrangement kind 'one_norm_parallel'.*pre_norm"):
             tb.load(folder, dtype="float32", max_tokens=128)
     finally:
-        ARRANGEMENTS.register("parallel", ParallelBlock)
+        ARRANGEMENTS.register("one_norm_parallel", ParallelBlock)
