@@ -41,6 +41,80 @@ pair_add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ d1, const T
     }
 }
 
+// The same with four neighbouring entries a thread and access (16 bytes of the float stream and of float inputs, 8
+// of 16-bit ones), where the sizes and addresses allow it.
+template <typename T>
+__device__ __forceinline__ float4 ld4f(const T* p) {
+    if constexpr (sizeof(T) == 2) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    } else {
+        return *reinterpret_cast<const float4*>(p);
+    }
+}
+template <typename T>
+__device__ __forceinline__ void st4f(T* p, float4 v) {
+    if constexpr (sizeof(T) == 2) {
+        uint2 raw;
+        *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+        *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+        *reinterpret_cast<uint2*>(p) = raw;
+    } else {
+        *reinterpret_cast<float4*>(p) = v;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+pair_add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ d1, const T* __restrict__ d2,
+                            const int* __restrict__ rows, const float* __restrict__ w1, T* __restrict__ y1, int ld1,
+                            const float* __restrict__ w2, T* __restrict__ y2, int ld2, float eps, int d) {
+    pdl_sync();
+    extern __shared__ __align__(16) float row_s[];
+    __shared__ float red[33];
+    const int i = blockIdx.x;
+    const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+    float ss = 0.f;
+    for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+        float4 add = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (d1) add = ld4f(d1 + r * d + c);
+        if (d2) {
+            const float4 b = ld4f(d2 + r * d + c);
+            add.x += b.x; add.y += b.y; add.z += b.z; add.w += b.w;
+        }
+        float4 v = *reinterpret_cast<const float4*>(x + r * d + c);
+        v.x += add.x; v.y += add.y; v.z += add.z; v.w += add.w;
+        if (!rows && (d1 || d2)) *reinterpret_cast<float4*>(x + r * d + c) = v;
+        *reinterpret_cast<float4*>(row_s + c) = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    if (!y1 && !y2) return;
+    const bool normed = w1 || w2;
+    float rs = 1.f;
+    if (normed) rs = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
+    for (int c = threadIdx.x * 4; c < d; c += blockDim.x * 4) {
+        const float4 v = *reinterpret_cast<const float4*>(row_s + c);
+        if (y1) {
+            float4 o = v;
+            if (w1) {
+                const float4 w = *reinterpret_cast<const float4*>(w1 + c);
+                o = make_float4(v.x * rs * w.x, v.y * rs * w.y, v.z * rs * w.z, v.w * rs * w.w);
+            }
+            st4f(y1 + (size_t)i * ld1 + c, o);
+        }
+        if (y2) {
+            float4 o = v;
+            if (w2) {
+                const float4 w = *reinterpret_cast<const float4*>(w2 + c);
+                o = make_float4(v.x * rs * w.x, v.y * rs * w.y, v.z * rs * w.z, v.w * rs * w.w);
+            }
+            st4f(y2 + (size_t)i * ld2 + c, o);
+        }
+    }
+}
+
 // ---- causal convolution over time ------------------------------------------------------------------------
 // y[t, c] = (residual ? u[t, c] : 0) + sum_j w[c, j] * u[t - taps + 1 + j, c]; the inputs before a step's first
 // token come from the sequence's state, [taps - 1, C] floats, oldest first (zeros when the sequence starts).
@@ -228,8 +302,16 @@ extern "C" {
         if (n_out < 0 || d <= 0 || d > 48 * 1024 / 4) return TB_ERR_ARG;                                              \
         if ((y1 && ld1 < d) || (y2 && ld2 < d) || (w1 && !y1) || (w2 && !y2)) return TB_ERR_ARG;                      \
         if (n_out == 0) return 0;                                                                                     \
-        TB_LAUNCH((pair_add_rmsnorm_kernel<T>), n_out, 256, (size_t)d * 4, s, x, (const T*)d1, (const T*)d2, rows,    \
-                  w1, (T*)y1, ld1, w2, (T*)y2, ld2, eps, d);                                                          \
+        const uintptr_t in_al = 4 * sizeof(T);                                                                        \
+        const bool vec = d % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)d1 % in_al == 0 &&                        \
+                         (uintptr_t)d2 % in_al == 0 && (uintptr_t)y1 % in_al == 0 && (uintptr_t)y2 % in_al == 0 &&    \
+                         ld1 % 4 == 0 && ld2 % 4 == 0 && (uintptr_t)w1 % 16 == 0 && (uintptr_t)w2 % 16 == 0;          \
+        if (vec)                                                                                                      \
+            TB_LAUNCH((pair_add_rmsnorm_vec_kernel<T>), n_out, 256, (size_t)d * 4, s, x, (const T*)d1, (const T*)d2,  \
+                      rows, w1, (T*)y1, ld1, w2, (T*)y2, ld2, eps, d);                                                \
+        else                                                                                                          \
+            TB_LAUNCH((pair_add_rmsnorm_kernel<T>), n_out, 256, (size_t)d * 4, s, x, (const T*)d1, (const T*)d2, rows,\
+                      w1, (T*)y1, ld1, w2, (T*)y2, ld2, eps, d);                                                      \
         return tb_last_error();                                                                                       \
     }                                                                                                                 \
     int tb_causal_conv_##SFX(const void* u, int ldu, const float* w, float* state, long long state_pitch, void* y,    \
