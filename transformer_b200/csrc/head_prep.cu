@@ -12,10 +12,13 @@
 //
 // A warp takes ONE head (a query, key or value head) of a tile of consecutive tokens; a lane holds the pairs
 // (2i, 2i + 1), i = lane, lane + 32, ..., of that head in registers from the convolution to the store, so nothing
-// waits on another warp.  A block is four heads; the convolution's weights of a head wait in shared memory, taps
-// major, so that a tile of tokens reads them from there (when they fit).  The host picks the tile: one token when a
-// step has few (decoding: every (token, head) its own warp), eight in a prompt.  In a step of one token per
-// sequence the warp also moves the convolution's state on; after any other step tb_conv_roll does.
+// waits on another warp.  A block is four heads.  Two forms:
+//   head_prep_kernel       any number of taps and any head sizes; one token a warp when a step has few (decoding:
+//                          every (token, head) its own warp, which also moves the convolution's state on), else
+//                          eight in turn with the head's weights waiting in shared memory, taps major
+//   head_prep_tile_kernel  steps of many tokens, 1 to 4 taps, even head sizes: the taps and the pairs per lane are
+//                          template parameters, HP_TILE tokens a warp, the window of earlier inputs in registers
+// After a step that is not one token per sequence tb_conv_roll moves the state on.
 #include "common.cuh"
 
 constexpr int HP_WARPS = 4;
@@ -379,7 +382,7 @@ extern "C" {
         if (dk > 64 * HP_PAIRS || dv > 64 * HP_PAIRS) return TB_ERR_UNSUPPORTED;                                      \
         if (nt == 0) return 0;                                                                                        \
         const int heads = nh + 2 * nkvh, groups = (heads + HP_WARPS - 1) / HP_WARPS;                                  \
-        /* a tile of eight tokens in a step of many; else one token a warp */                                         \
+        /* the general form: eight tokens a warp in a step of many, else one */                                        \
         const int tile = nt >= 64 ? 8 : 1;                                                                            \
         size_t smem = conv ? (size_t)HP_WARPS * taps * (dk > dv ? dk : dv) * 4 : 0;                       \
         const int staged = smem > 0 && smem <= 48 * 1024 && tile > 1;                                                 \
