@@ -382,6 +382,32 @@ def test_a_sink_takes_its_share_of_the_softmax():
     assert float((got2.abs() - got.abs()).max()) < 0          # every entry shrank
 
 
+@pytest.mark.parametrize("kernel, H, rank, rot", [("float32", 3, 48, 8), ("bfloat16", 8, 128, 16), ("mma1", 8, 128, 32),
+                                                  ("mma3", 4, 256, 64), ("mma7", 16, 512, 64)])
+def test_causal_latent_kernels_reach_the_first_key_and_keys_far_back(kernel, H, rank, rot):
+    """The latent attention without a window (the design's form): every head of every query asks, far above the
+    rest, for the sequence's first key, for one 300 tokens back among hundreds, and for the keys on both sides of
+    a page border; general and tensor-core kernels, the keys whole and in slices, prompts and single tokens."""
+    from test_salepel_gpu import _latent_attention
+    causal = 1 << 30            # what the part hands the kernels for "no window"
+    dtype = kernel if not kernel.startswith("mma") else "bfloat16"
+    splits = int(kernel[3:]) if kernel.startswith("mma") else 0
+
+    def keys(b, n, g):
+        k = torch.randn(n, rank + rot, generator=g)
+        return k / k.norm(dim=1, keepdim=True)
+
+    for which in ("first", "300 back", "page row 63", "page row 64"):
+        def queries(b, p, k, g, which=which):
+            j = {"first": 0, "300 back": p - 300, "page row 63": (p // 64) * 64 - 1, "page row 64": (p // 64) * 64}[which]
+            j = min(max(j, 0), p)
+            return (k[j] * 160.0).float().repeat(H, 1)
+        got, want = _latent_attention(dtype, H, rank, rot, causal, [0, 390, 64, 700], [70, 1, 1, 2], queries, keys,
+                                      splits=splits)
+        tol = 1e-4 if dtype == "float32" else 2e-2
+        assert float((got - want).abs().max()) <= tol, f"{which}: {float((got - want).abs().max()):.3e}"
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("d", [48, 50, 320, 4096])
 def test_pair_sum_and_two_norms_in_one_kernel(dtype, d):
