@@ -255,36 +255,43 @@ __global__ void __launch_bounds__(HP_WARPS * 32, PAIRS <= 2 ? 6 : 3) head_prep_t
             if (t0 + tt < a.nt && 2 * i < dim)
                 ld2<T, true>(z + (size_t)(t0 + tt) * a.ldz + coff + 2 * i, true, own[tt][r].x, own[tt][r].y);
         }
+    // The rows before the tile are asked for with the tile's own, before it is known whether they are the same
+    // sequence's: where they are not, the state's rows take their place below.
+    float2 hist[HIST][PAIRS];                          // hist[k]: the input k + 1 tokens back
+#pragma unroll
+    for (int k = 0; k < HIST; ++k)
+#pragma unroll
+        for (int r = 0; r < PAIRS; ++r) {
+            const int i = lane + 32 * r;
+            hist[k][r] = make_float2(0.f, 0.f);
+            if (TAPS > 1 && 2 * i < dim && t0 - (k + 1) >= 0)
+                ld2<T, true>(z + (size_t)(t0 - (k + 1)) * a.ldz + coff + 2 * i, true, hist[k][r].x, hist[k][r].y);
+        }
     // where each of the tile's tokens stands: lane tt looks it up, every lane asks that lane
     static_assert(TILE <= 32, "a lane per token of the tile");
-    int my_pos = 0, my_page = 0, my_slot = 0, my_first = 0;
+    int my_pos = 0, my_page = 0, my_slot = 0, my_tl = 1 << 20;
     if (lane < TILE && t0 + lane < a.nt) {
         const int b = a.tok_seq[t0 + lane];
         my_pos = a.tok_pos[t0 + lane];
-        my_first = t0 + lane == a.seq_start[b];
+        my_tl = t0 + lane - a.seq_start[b];           // 0: the first token of its sequence's portion
         my_slot = a.slots ? a.slots[b] : 0;
         if (kind != 0) my_page = a.page_table[(size_t)b * a.max_pages + my_pos / TB_PAGE];
     }
-    float2 hist[HIST][PAIRS];                          // hist[k]: the input k + 1 tokens back
     if constexpr (TAPS > 1) {
-        const int b = a.tok_seq[t0];
-        const int tl = t0 - a.seq_start[b];
-        const float* st = a.state + (size_t)__shfl_sync(0xffffffffu, my_slot, 0) * a.state_pitch;
+        const int tl = __shfl_sync(0xffffffffu, my_tl, 0);
+        if (tl < TAPS - 1) {                           // the portion starts so shortly before the tile: the older inputs are state
+            const float* st = a.state + (size_t)__shfl_sync(0xffffffffu, my_slot, 0) * a.state_pitch;
 #pragma unroll
-        for (int k = 0; k < TAPS - 1; ++k)
+            for (int k = 0; k < TAPS - 1; ++k)
 #pragma unroll
-            for (int r = 0; r < PAIRS; ++r) {
-                const int i = lane + 32 * r;
-                hist[k][r] = make_float2(0.f, 0.f);
-                if (2 * i >= dim) continue;
-                const int back = k + 1, c = coff + 2 * i;
-                if (tl - back >= 0) {
-                    ld2<T, true>(z + (size_t)(t0 - back) * a.ldz + c, true, hist[k][r].x, hist[k][r].y);
-                } else {
-                    const float* sp = st + (size_t)(TAPS - 1 + tl - back) * C + c;
+                for (int r = 0; r < PAIRS; ++r) {
+                    const int i = lane + 32 * r;
+                    const int back = k + 1;
+                    if (2 * i >= dim || tl - back >= 0) continue;
+                    const float* sp = st + (size_t)(TAPS - 1 + tl - back) * C + coff + 2 * i;
                     hist[k][r] = make_float2(sp[0], sp[1]);
                 }
-            }
+        }
     }
 #pragma unroll
     for (int tt = 0; tt < TILE; ++tt) {
@@ -292,7 +299,7 @@ __global__ void __launch_bounds__(HP_WARPS * 32, PAIRS <= 2 ? 6 : 3) head_prep_t
         if (t >= a.nt) break;
         const int pos = __shfl_sync(0xffffffffu, my_pos, tt);
         if constexpr (TAPS > 1) {
-            const int first = __shfl_sync(0xffffffffu, my_first, tt), slot = __shfl_sync(0xffffffffu, my_slot, tt);
+            const int first = __shfl_sync(0xffffffffu, my_tl, tt) == 0, slot = __shfl_sync(0xffffffffu, my_slot, tt);
             if (tt > 0 && first) {                      // another sequence's portion starts here
                 const float* st = a.state + (size_t)slot * a.state_pitch;
 #pragma unroll
