@@ -1,2 +1,2 @@
 """Architectures known to the registry.  Importing this package registers them."""
-from . import dumalix, llama, salepel, zufadra  # noqa: F401
+from . import dumalix, fugavik, llama, salepel, zufadra  # noqa: F401

@@ -1,4 +1,5 @@
-// Biases of a feed-forward whose projections have them, applied to the products' results.
+// Biases of a feed-forward whose projections have them, applied to the products' results; and the squared relu of
+// a feed-forward without a gate.
 //
 //   h[t, c] = silu(gu[t, c] + b[c]) * (gu[t, di + c] + b[di + c])        the (gate, up) pair with its biases
 // Biases are float; the sums and the activation are float, one rounding at the store.
@@ -52,6 +53,30 @@ __global__ void __launch_bounds__(256) bias_glu_vec_kernel(const T* __restrict__
     }
 }
 
+// h[i] = max(h[i], 0)^2 in place: the activation of a feed-forward without a gate, on its first product's result
+template <typename T>
+__global__ void __launch_bounds__(256) relu2_kernel(T* __restrict__ h, long long n) {
+    pdl_sync();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float v = fmaxf(ldf(h + i), 0.f);
+        stf(h + i, v * v);
+    }
+}
+template <typename T>
+__global__ void __launch_bounds__(256) relu2_vec_kernel(T* __restrict__ h, long long n8) {
+    pdl_sync();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+        float v[8];
+        load8(h + i * 8, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            v[e] = fmaxf(v[e], 0.f);
+            v[e] *= v[e];
+        }
+        store8(h + i * 8, v);
+    }
+}
+
 static int grid_for(long long n) {
     const long long blocks = (n + 255) / 256;
     return (int)(blocks > 8192 ? 8192 : blocks);
@@ -71,8 +96,22 @@ extern "C" {
     }
 TB_BIAS(f32, float)
 TB_BIAS(bf16, __nv_bfloat16)
+#define TB_RELU2(SFX, T)                                                                                              \
+    int tb_relu2_##SFX(void* h, long long n, cudaStream_t s) {                                                        \
+        if (n < 0 || (n && !h)) return TB_ERR_ARG;                                                                    \
+        if (n == 0) return 0;                                                                                         \
+        if (n % 8 == 0 && ((uintptr_t)h & 15) == 0)                                                                   \
+            TB_LAUNCH((relu2_vec_kernel<T>), grid_for(n / 8), 256, 0, s, (T*)h, n / 8);                               \
+        else                                                                                                          \
+            TB_LAUNCH((relu2_kernel<T>), grid_for(n), 256, 0, s, (T*)h, n);                                           \
+        return tb_last_error();                                                                                       \
+    }
+TB_RELU2(f32, float)
+TB_RELU2(bf16, __nv_bfloat16)
 }
 
 #include "tape.h"
 TB_TAPE_REGISTER(tb_bias_glu_f32)
 TB_TAPE_REGISTER(tb_bias_glu_bf16)
+TB_TAPE_REGISTER(tb_relu2_f32)
+TB_TAPE_REGISTER(tb_relu2_bf16)

@@ -49,6 +49,8 @@ struct DeltaPrepArgs {
     const int* slots;
     long long state_stride, conv_offset;
     int ldz, G, H, dim, vdim, taps, update_state;
+    int lda, ldb;           // row pitches of a and bz (floats)
+    int head_decay;         // 1: one decay per head: a [nt, H], dt_bias [H], the same g for every key channel
 };
 
 __device__ __forceinline__ float cd_softplus(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
@@ -140,12 +142,17 @@ __global__ void __launch_bounds__(32 * CD_PT) delta_prep_kernel(const DeltaPrepA
             for (int c = lane; c < DP; c += 32) r[DP + c] = c < dim ? y[dim + c] * ik : 0.f;
         } else if (piece == 2) {
             const float rate = expf(p.A_log[hh]);
-            const float* a = p.a + (size_t)t * p.H * dim + (size_t)hh * dim;
-            const float* db = p.dt_bias + (size_t)hh * dim;
-            for (int c = lane; c < DP; c += 32) r[2 * DP + c] = c < dim ? expf(-rate * cd_softplus(a[c] + db[c])) : 1.f;
+            if (p.head_decay) {
+                const float gh = expf(-rate * cd_softplus(p.a[(size_t)t * p.lda + hh] + p.dt_bias[hh]));
+                for (int c = lane; c < DP; c += 32) r[2 * DP + c] = c < dim ? gh : 1.f;
+            } else {
+                const float* a = p.a + (size_t)t * p.lda + (size_t)hh * dim;
+                const float* db = p.dt_bias + (size_t)hh * dim;
+                for (int c = lane; c < DP; c += 32) r[2 * DP + c] = c < dim ? expf(-rate * cd_softplus(a[c] + db[c])) : 1.f;
+            }
         } else {
             if (lane < 4)
-                r[3 * DP + lane] = lane == 0 ? 1.0f / (1.0f + expf(-p.bz[(size_t)t * p.H + hh])) : lane == 1 ? stats[tt][2] : 0.f;
+                r[3 * DP + lane] = lane == 0 ? 1.0f / (1.0f + expf(-p.bz[(size_t)t * p.ldb + hh])) : lane == 1 ? stats[tt][2] : 0.f;
             float* vb = p.vbuf + ((size_t)t * p.H + hh) * VP;
             for (int c = lane; c < VP; c += 32) vb[c] = c < vdim ? y[2 * dim + h * vdim + c] : 0.f;
         }
@@ -353,10 +360,12 @@ int tb_delta_value_pitch(int vdim) { return cd_vpitch(vdim); }
     int tb_delta_prep_##SFX(const void* z, int ldz, const float* wconv, float* state, const float* a,                 \
                             const float* dt_bias, const float* A_log, const float* bz, float* rec, float* vbuf,       \
                             const int* tok_seq, const int* seq_start, const int* slots, int nt, int B, int G, int H,  \
-                            int dim, int vdim, int taps, int update_state, cudaStream_t s) {                          \
+                            int dim, int vdim, int taps, int update_state, int lda, int ldb, int head_decay,          \
+                            cudaStream_t s) {                                                                         \
+        if (lda < (head_decay ? H : H * dim) || ldb < H) return TB_ERR_ARG;                                           \
         DeltaPrepArgs p{z, wconv, state, a, dt_bias, A_log, bz, rec, vbuf, tok_seq, seq_start, slots,                 \
                         (long long)tb_delta_state_size(G, H, dim, vdim, taps), (long long)H * dim * vdim, ldz, G, H,  \
-                        dim, vdim, taps, update_state};                                                               \
+                        dim, vdim, taps, update_state, lda, ldb, head_decay ? 1 : 0};                                 \
         return delta_prep_launch<T>(p, nt, B, s);                                                                     \
     }
 TB_DELTA_PREP(f32, float)

@@ -260,11 +260,12 @@ add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const
     }
     __syncthreads();
     if (warp == 0) {
-        if (tail.rule.scored)
+        if (tail.rule.scored == 1)
             router_pick_scored(lg, lg + tail.E, tail.rule.bias, tail.idx + (size_t)i * tail.k,
                                tail.wts + (size_t)i * tail.k, tail.E, tail.k, lane);
         else
-            router_pick(lg, tail.idx + (size_t)i * tail.k, tail.wts + (size_t)i * tail.k, tail.E, tail.k, lane);
+            router_pick(lg, tail.idx + (size_t)i * tail.k, tail.wts + (size_t)i * tail.k, tail.E, tail.k, lane,
+                        tail.rule.scored == 2);
     }
 }
 
@@ -353,11 +354,12 @@ post_add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, cons
     }
     __syncthreads();
     if (warp == 0) {
-        if (tail.rule.scored)
+        if (tail.rule.scored == 1)
             router_pick_scored(lg, lg + tail.E, tail.rule.bias, tail.idx + (size_t)i * tail.k,
                                tail.wts + (size_t)i * tail.k, tail.E, tail.k, lane);
         else
-            router_pick(lg, tail.idx + (size_t)i * tail.k, tail.wts + (size_t)i * tail.k, tail.E, tail.k, lane);
+            router_pick(lg, tail.idx + (size_t)i * tail.k, tail.wts + (size_t)i * tail.k, tail.E, tail.k, lane,
+                        tail.rule.scored == 2);
     }
 }
 
@@ -438,7 +440,7 @@ static int add_rmsnorm_launch(float* x, const void* delta, const void* wy, const
     if (n_out == 0) return 0;
     if (tail.w) {
         // the form that also routes: a few rows, a width of 16-byte pieces, the row and the logits in 40 KB
-        const size_t smem = (size_t)d * sizeof(T) + (size_t)tail.E * sizeof(float) * (tail.rule.scored ? 2 : 1);
+        const size_t smem = (size_t)d * sizeof(T) + (size_t)tail.E * sizeof(float) * (tail.rule.scored == 1 ? 2 : 1);
         if (d % 8 || d > 512 * 8 * NORM_CHUNKS || n_out > 256 || smem > 40 * 1024 ||
             (reinterpret_cast<uintptr_t>(tail.w) & 15))
             return TB_ERR_UNSUPPORTED;           // the caller runs the router by itself

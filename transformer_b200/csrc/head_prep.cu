@@ -4,6 +4,9 @@
 //   u = causal convolution over time of every channel of [q | k | v]     (taps wide, the last inputs kept per sequence)
 //   q_h <- u_q,h / rms(u_q,h) * wq * temp_h,   k_g <- u_k,g / rms(u_k,g) * wk        (weights of one head, shared)
 //   the first rdims entries of every query and key head turn by position * f_i in the pairs (2i, 2i + 1)
+//   v <- (1 - l) v + l v_source      a blend with the values that an earlier layer left for the same token in
+//                                    `vfirst` (float [nt, nkvh * dv]); without `vmix` (the number l) this layer is
+//                                    that source and leaves its own values there
 //   every pair (2m, 2m + 1) of a value head turns by position * g_m
 //   queries go to `qout`, keys and values into the paged cache
 //
@@ -47,6 +50,8 @@ struct HeadPrepArgs {
     const int* page_table;
     int max_pages, ldz, nt, nh, nkvh, dk, dv, rdims, taps, decode, tok_tile, staged;
     float eps;
+    float* vfirst;          // [nt, nkvh * dv] or null: the values of the blend's source
+    const float* vmix;      // one number, or null
 };
 
 // two neighbouring entries, as one access where the layout allows it
@@ -162,6 +167,23 @@ __global__ void __launch_bounds__(HP_WARPS * 32) head_prep_kernel(const HeadPrep
             x0[r] = a0;
             x1[r] = a1;
             ss += a0 * a0 + a1 * a1;
+        }
+        if (kind == 2 && a.vfirst) {
+            float* vf = a.vfirst + ((size_t)t * a.nkvh + (h - a.nh - a.nkvh)) * a.dv;
+            const float lam = a.vmix ? *a.vmix : 0.f;
+#pragma unroll
+            for (int r = 0; r < HP_PAIRS; ++r) {
+                const int i = lane + 32 * r;
+                if (2 * i >= dim) continue;
+                const bool two = 2 * i + 1 < dim;
+                if (a.vmix) {
+                    x0[r] = (1.f - lam) * x0[r] + lam * vf[2 * i];
+                    if (two) x1[r] = (1.f - lam) * x1[r] + lam * vf[2 * i + 1];
+                } else {
+                    vf[2 * i] = x0[r];
+                    if (two) vf[2 * i + 1] = x1[r];
+                }
+            }
         }
         T* dst;
         if (kind == 0) {
@@ -329,6 +351,23 @@ __global__ void __launch_bounds__(HP_WARPS * 32, PAIRS <= 2 ? 6 : 3) head_prep_t
             x1[r] = a1;
             ss += a0 * a0 + a1 * a1;
         }
+        if (kind == 2 && a.vfirst) {
+            float* vf = a.vfirst + ((size_t)t * a.nkvh + (h - a.nh - a.nkvh)) * a.dv;
+            const float lam = a.vmix ? __ldg(a.vmix) : 0.f;
+#pragma unroll
+            for (int r = 0; r < PAIRS; ++r) {
+                const int i = lane + 32 * r;
+                if (2 * i >= dim) continue;
+                float2* at = reinterpret_cast<float2*>(vf + 2 * i);
+                if (a.vmix) {
+                    const float2 f = *at;
+                    x0[r] = (1.f - lam) * x0[r] + lam * f.x;
+                    x1[r] = (1.f - lam) * x1[r] + lam * f.y;
+                } else {
+                    *at = make_float2(x0[r], x1[r]);
+                }
+            }
+        }
         if constexpr (TAPS > 1) {
 #pragma unroll
             for (int k = TAPS - 2; k > 0; --k)
@@ -379,11 +418,12 @@ extern "C" {
                            const float* sinT, const float* vcos, const float* vsin, void* qout, void* kc, void* vc,   \
                            const int* tok_seq, const int* tok_pos, const int* seq_start, const int* slots,            \
                            const int* page_table, int max_pages, int nt, int nh, int nkvh, int dk, int dv, int rdims, \
-                           int taps, int decode, cudaStream_t s) {                                                    \
+                           int taps, int decode, float* vfirst, const float* vmix, cudaStream_t s) {                  \
         if (nt < 0 || nh <= 0 || nkvh <= 0 || dk <= 0 || dv <= 0 || rdims < 0 || rdims > dk || rdims % 2)             \
             return TB_ERR_ARG;                                                                                        \
         if (taps < 1 || taps > 16 || (conv && taps > 1 && !state) || (rdims && (!cosT || !sinT))) return TB_ERR_ARG;  \
         if (vcos && (dv % 2 || !vsin)) return TB_ERR_ARG;                                                             \
+        if (vmix && !vfirst) return TB_ERR_ARG;                                                                       \
         const long long C = (long long)(nh + nkvh) * dk + (long long)nkvh * dv;                                       \
         if (ldz < C || (conv && taps > 1 && state_pitch < (taps - 1) * C)) return TB_ERR_ARG;                         \
         if (dk > 64 * HP_PAIRS || dv > 64 * HP_PAIRS) return TB_ERR_UNSUPPORTED;                                      \
@@ -396,11 +436,11 @@ extern "C" {
         if (!staged) smem = 0;                                                                                        \
         HeadPrepArgs a{z, conv, state, state_pitch, wq, wk, temp, cosT, sinT, vcos, vsin, qout, kc, vc, tok_seq,      \
                        tok_pos, seq_start, slots, page_table, max_pages, ldz, nt, nh, nkvh, dk, dv, rdims, taps,      \
-                       decode ? 1 : 0, tile, staged, eps};                                                            \
+                       decode ? 1 : 0, tile, staged, eps, vfirst, vmix};                                              \
         const size_t es = sizeof(T);                                                                                  \
         const bool vec = dk % 2 == 0 && dv % 2 == 0 && ldz % 2 == 0 && (uintptr_t)z % (2 * es) == 0 &&                \
                          (uintptr_t)qout % (2 * es) == 0 && (uintptr_t)kc % (2 * es) == 0 &&                          \
-                         (uintptr_t)vc % (2 * es) == 0;                                                               \
+                         (uintptr_t)vc % (2 * es) == 0 && (uintptr_t)vfirst % 8 == 0;                                 \
         const int taps_eff = conv ? taps : 1;                                                                         \
         if (vec && tile == 8 && !decode && taps_eff <= 4 && (uintptr_t)conv % 8 == 0) {                               \
             const int dmax = dk > dv ? dk : dv;                                                                       \

@@ -90,6 +90,9 @@ struct LatentArgs {
     const float* sinT;
     int max_pages, ldq, q_head, q_plain, H, rank, rot, rdims, window, heads_per_block, tokens_per_block;
     float scale;
+    const float* sinks;     // [H] or null: a number per head that joins the softmax's denominator once
+    const void* gate;       // [nt, ldg] or null: head h's output is multiplied by sigmoid(gate[t, h])
+    int ldg;
 };
 
 template <typename T, int NV>
@@ -217,7 +220,14 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(const L
         if (!live[rr]) continue;
         const int row = warp * LA_RPW + rr;
         const int t = t0 + row / hc, h = h0 + row % hc;
-        const float inv = sum[rr] > 0.f ? 1.0f / sum[rr] : 0.f;
+        float f = 1.f, l = sum[rr];
+        if (a.sinks) {          // the sink has no key and no value: it only enters the maximum and the sum
+            const float sk = a.sinks[h], m2 = fmaxf(mx[rr], sk);
+            f = mx[rr] > -INFINITY ? expf(mx[rr] - m2) : 0.f;
+            l = l * f + expf(sk - m2);
+        }
+        float inv = l > 0.f ? f / l : 0.f;
+        if (a.gate) inv *= 1.0f / (1.0f + expf(-ldf(static_cast<const T*>(a.gate) + (size_t)t * a.ldg + h)));
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const int c = lane + 32 * i;
@@ -281,9 +291,9 @@ int tb_latent_attention_tile_tokens(int H) {
                                   const int* tile_t0, const int* tile_nq, const int* tok_pos, const int* page_table,  \
                                   const float* cosT, const float* sinT, int tiles, int max_pages, int ldq,            \
                                   int q_head, int q_plain, int H, int rank, int rot, int rdims, int window,           \
-                                  float scale, cudaStream_t s) {                                                      \
+                                  float scale, const float* sinks, const void* gate, int ldg, cudaStream_t s) {       \
         LatentArgs a{qa, q, out, cache, tile_seq, tile_t0, tile_nq, tok_pos, page_table, cosT, sinT, max_pages, ldq,  \
-                     q_head, q_plain, H, rank, rot, rdims, window, 0, 0, scale};                                      \
+                     q_head, q_plain, H, rank, rot, rdims, window, 0, 0, scale, sinks, gate, ldg};                    \
         return latent_attention_launch<T>(a, tiles, s);                                                               \
     }
 TB_LATENT(f32, float)

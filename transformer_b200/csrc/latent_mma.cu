@@ -37,7 +37,24 @@ struct LatentMmaArgs {
     const float* sinT;
     int max_pages, ldq, q_head, q_plain, H, rank, rot, rdims, window, heads_per_block, tokens_per_block, splits;
     float scale;
+    const float* sinks;          // [H] or null: a number per head that joins the softmax's denominator once
+    const __nv_bfloat16* gate;   // [nt, ldg] or null: head h's output is multiplied by sigmoid(gate[t, h])
+    int ldg;
 };
+
+// What a sink and a gate make of a row's (maximum, sum): the factor for its unnormalized output.
+__device__ __forceinline__ float lm_finish(float m, float l, const float* sinks, const __nv_bfloat16* gate, int ldg,
+                                           int t, int h) {
+    float f = 1.f;
+    if (sinks) {
+        const float sk = sinks[h], m2 = fmaxf(m, sk);
+        f = m > -INFINITY ? __expf(m - m2) : 0.f;
+        l = l * f + __expf(sk - m2);
+    }
+    f = l > 0.f ? f / l : 0.f;
+    if (gate) f *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[(size_t)t * ldg + h])));
+    return f;
+}
 
 __device__ __forceinline__ void lm_ldmatrix_x4(unsigned (&r)[4], const void* p) {
     const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
@@ -283,7 +300,7 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_mma_kernel(const LatentM
         const int t = t0 + row / hc, h = h0 + row % hc;
         const float l = sum_s[row];
         if (a.splits == 1) {
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            const float inv = lm_finish(max_s[row], l, a.sinks, a.gate, a.ldg, t, h);
             __nv_bfloat16* o = a.out + ((size_t)t * a.H + h) * a.rank + warp * cols_w;
 #pragma unroll
             for (int i = 0; i < NT; ++i) {
@@ -314,7 +331,8 @@ __global__ void __launch_bounds__(LM_WARPS * 32) latent_mma_kernel(const LatentM
 // once, then every thread its columns with the loads of all slices in flight together
 #define LM_MAX_SPLITS 16
 __global__ void __launch_bounds__(128)
-latent_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int splits, int rank) {
+latent_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int splits, int rank,
+                    const float* __restrict__ sinks, const __nv_bfloat16* __restrict__ gate, int ldg, int H) {
     pdl_sync();
     __shared__ float f_s[LM_MAX_SPLITS];
     const float* p = partial + (size_t)blockIdx.x * splits * (rank + 2);
@@ -325,7 +343,8 @@ latent_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict
         const float m = warp_max(ms);
         const float f = ms > -INFINITY ? __expf(ms - m) : 0.f;
         const float l = warp_sum(f * ls);
-        if (lane < splits) f_s[lane] = l > 0.f ? f / l : 0.f;
+        const float fin = lm_finish(m, l, sinks, gate, ldg, blockIdx.x / H, blockIdx.x % H);
+        if (lane < splits) f_s[lane] = f * fin;
     }
     __syncthreads();
     for (int c = threadIdx.x; c < rank; c += blockDim.x) {
@@ -360,7 +379,8 @@ int tb_latent_attention_mma_bf16(const void* qa, const void* q, void* out, float
                                  const int* tile_seq, const int* tile_t0, const int* tile_nq, const int* tok_pos,
                                  const int* page_table, const float* cosT, const float* sinT, int tiles, int nt,
                                  int max_pages, int ldq, int q_head, int H, int rank, int rot, int rdims, int window,
-                                 int splits, float scale, cudaStream_t s) {
+                                 int splits, float scale, const float* sinks, const void* gate, int ldg,
+                                 cudaStream_t s) {
     const int q_plain = q_head - rot;      // a head's queries: the plain entries, then the rotated ones
     if (tiles < 0 || nt < 0 || H <= 0 || rank <= 0 || rot < 0 || window <= 0 || rdims < 0 || rdims > rot || rdims % 2 ||
         splits < 1 || splits > LM_MAX_SPLITS || (splits > 1 && !partial))
@@ -371,7 +391,8 @@ int tb_latent_attention_mma_bf16(const void* qa, const void* q, void* out, float
     const int hc = H < LM_ROWS ? H : LM_ROWS;
     LatentMmaArgs a{(const __nv_bfloat16*)qa, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, partial,
                     (const __nv_bfloat16*)cache, tile_seq, tile_t0, tile_nq, tok_pos, page_table, cosT, sinT, max_pages,
-                    ldq, q_head, q_plain, H, rank, rot, rdims, window, hc, LM_ROWS / hc, splits, scale};
+                    ldq, q_head, q_plain, H, rank, rot, rdims, window, hc, LM_ROWS / hc, splits, scale, sinks,
+                    (const __nv_bfloat16*)gate, ldg};
     const int DK = rank + rot, pitch = DK + 8;
     const size_t smem = (size_t)(LM_ROWS + LM_KEYS) * pitch * 2 + LM_ROWS * (LM_KEYS + 1) * 4 + LM_ROWS * (LM_KEYS + 8) * 2 +
                         2 * LM_ROWS * 4 + LM_ROWS * 4;
@@ -390,7 +411,8 @@ int tb_latent_attention_mma_bf16(const void* qa, const void* q, void* out, float
         else rc = latent_mma_go<16, 4>(a, tiles, smem, s);
     }
     if (rc || splits == 1) return rc;
-    TB_LAUNCH((latent_merge_kernel), nt * H, 128, 0, s, (const float*)partial, (__nv_bfloat16*)out, splits, rank);
+    TB_LAUNCH((latent_merge_kernel), nt * H, 128, 0, s, (const float*)partial, (__nv_bfloat16*)out, splits, rank, sinks,
+              (const __nv_bfloat16*)gate, ldg, H);
     return tb_last_error();
 }
 }

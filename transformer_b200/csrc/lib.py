@@ -56,10 +56,10 @@ _SIGNATURES: Dict[str, str] = {
     "tb_moe_identity_rows_f32": "pppppiiii", "tb_moe_identity_rows_bf16": "pppppiiii",
     "tb_mlstm_scan_f32": "pppppppiiiiiff", "tb_mlstm_scan_bf16": "pppppppiiiiiff",
     "tb_mlstm_chunk_f32": "pppppppiiiiiff", "tb_mlstm_chunk_bf16": "pppppppiiiiiff",
-    "tb_mlstm_out_f32": "ppippiiif", "tb_mlstm_out_bf16": "ppippiiif",
+    "tb_mlstm_out_f32": "ppippiiifi", "tb_mlstm_out_bf16": "ppippiiifi",
     "tb_latent_prep_f32": "pippfpppppippiiiii", "tb_latent_prep_bf16": "pippfpppppippiiiii",
-    "tb_latent_attention_mma_bf16": "ppppppppppppiiiiiiiiiiif",
-    "tb_latent_attention_f32": "pppppppppppiiiiiiiiiif", "tb_latent_attention_bf16": "pppppppppppiiiiiiiiiif",
+    "tb_latent_attention_mma_bf16": "ppppppppppppiiiiiiiiiiifppi",
+    "tb_latent_attention_f32": "pppppppppppiiiiiiiiiifppi", "tb_latent_attention_bf16": "pppppppppppiiiiiiiiiifppi",
     "tb_embed_bigram_f32": "pppppppppiifiii", "tb_embed_bigram_bf16": "pppppppppiifiii",
     "tb_scale_f32": "plf",
     "tb_qknorm_rope_cache_f32": "pippfpppippppiiiiiii", "tb_qknorm_rope_cache_bf16": "pippfpppippppiiiiiii",
@@ -67,12 +67,17 @@ _SIGNATURES: Dict[str, str] = {
     "tb_pair_add_rmsnorm_f32": "ppppppippifii", "tb_pair_add_rmsnorm_bf16": "ppppppippifii",
     "tb_conv_roll_f32": "piplppiii", "tb_conv_roll_bf16": "piplppiii",
     "tb_causal_conv_f32": "pipplpipppiiiiii", "tb_causal_conv_bf16": "pipplpipppiiiiii",
-    "tb_head_prep_f32": "pipplpppfppppppppppppiiiiiiiii", "tb_head_prep_bf16": "pipplpppfppppppppppppiiiiiiiii",
+    "tb_head_prep_f32": "pipplpppfppppppppppppiiiiiiiiipp", "tb_head_prep_bf16": "pipplpppfppppppppppppiiiiiiiiipp",
     "tb_attention_window_mma_bf16": "pppppppppppiiiiiiiiiiiiffippp",
-    "tb_delta_prep_f32": "pipppppppppppiiiiiiii",
-    "tb_delta_prep_bf16": "pipppppppppppiiiiiiii",
+    "tb_delta_prep_f32": "pipppppppppppiiiiiiiiiii",
+    "tb_delta_prep_bf16": "pipppppppppppiiiiiiiiiii",
     "tb_delta_scan": "ppppppiiiiiii",
     "tb_bias_glu_f32": "pppiii", "tb_bias_glu_bf16": "pppiii",
+    "tb_router_sigmoid_f32": "ppppppppiiii", "tb_router_sigmoid_bf16": "ppppppppiiii",
+    "tb_router_rows_sigmoid_bf16": "ppppppppiiii",
+    "tb_moe_scaled_rows_f32": "ppppiii", "tb_moe_scaled_rows_bf16": "ppppiii",
+    "tb_relu2_f32": "pl", "tb_relu2_bf16": "pl",
+    "tb_post_add_layernorm_f32": "pppppippfipppfipii", "tb_post_add_layernorm_bf16": "pppppippfipppfipii",
 }
 class TapeArg(ctypes.Union):
     _fields_ = [("p", ctypes.c_void_p), ("i", ctypes.c_int), ("f", ctypes.c_float), ("l", ctypes.c_longlong),

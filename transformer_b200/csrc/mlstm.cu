@@ -470,7 +470,7 @@ static int mlstm_chunk_launch(const MlstmArgs& a, int B, cudaStream_t s) {
 template <typename T>
 __global__ void __launch_bounds__(128)
 mlstm_out_kernel(const float* __restrict__ o, const T* __restrict__ g, int ldg, const float* __restrict__ w,
-                 T* __restrict__ y, int nt, int H, int vdim, float eps) {
+                 T* __restrict__ y, int nt, int H, int vdim, float eps, int silu) {
     pdl_sync();
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -484,7 +484,9 @@ mlstm_out_kernel(const float* __restrict__ o, const T* __restrict__ g, int ldg, 
     const T* grow = g + (size_t)t * ldg + (size_t)h * vdim;
     T* yrow = y + (size_t)t * H * vdim + (size_t)h * vdim;
     for (int c = lane; c < vdim; c += 32) {
-        const float gate = 1.0f / (1.0f + expf(-ldf(grow + c)));
+        const float gz = ldf(grow + c);
+        float gate = 1.0f / (1.0f + expf(-gz));
+        if (silu) gate *= gz;
         stf(yrow + c, orow[c] * rs * w[(size_t)h * vdim + c] * gate);
     }
 }
@@ -522,10 +524,11 @@ int tb_mlstm_state_size(int dim, int vdim) {
         return mlstm_chunk_launch<T>(a, B, s);                                                                        \
     }                                                                                                                 \
     int tb_mlstm_out_##SFX(const float* o, const void* g, int ldg, const float* w, void* y, int nt, int H, int vdim,  \
-                           float eps, cudaStream_t s) {                                                               \
+                           float eps, int silu, cudaStream_t s) {                                                     \
         if (nt < 0 || H <= 0 || vdim <= 0) return TB_ERR_ARG;                                                         \
         if (nt == 0) return 0;                                                                                        \
-        TB_LAUNCH((mlstm_out_kernel<T>), (nt * H + 3) / 4, 128, 0, s, o, (const T*)g, ldg, w, (T*)y, nt, H, vdim, eps); \
+        TB_LAUNCH((mlstm_out_kernel<T>), (nt * H + 3) / 4, 128, 0, s, o, (const T*)g, ldg, w, (T*)y, nt, H, vdim, eps, \
+                  silu);                                                                                              \
         return tb_last_error();                                                                                       \
     }
 TB_MLSTM(f32, float)

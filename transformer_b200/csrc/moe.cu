@@ -94,10 +94,10 @@ router_kernel(const T* __restrict__ x1, const T* __restrict__ wr, int* __restric
     __syncthreads();
     if (warp != 0 && !lists.done) return;
     if (warp == 0) {
-        if (rule.scored)
+        if (rule.scored == 1)
             router_pick_scored(lg, lg + E, rule.bias, topk_idx + (size_t)t * k, topk_w + (size_t)t * k, E, k, lane);
         else
-            router_pick(lg, topk_idx + (size_t)t * k, topk_w + (size_t)t * k, E, k, lane);
+            router_pick(lg, topk_idx + (size_t)t * k, topk_w + (size_t)t * k, E, k, lane, rule.scored == 2);
     }
     if (!lists.done) return;
     __threadfence();          // this token's choice is visible before the count says so
@@ -198,7 +198,7 @@ router_rows_kernel(const __nv_bfloat16* __restrict__ x1, const __nv_bfloat16* __
         if (logits_out && row0 + r < nt && e < E) logits_out[(size_t)(row0 + r) * E + e] = v;
     }
     __syncthreads();
-    if (rule.scored) {       // a warp per token; the scores go where the second warp's partial sums were
+    if (rule.scored == 1) {  // a warp per token; the scores go where the second warp's partial sums were
         for (int r = warp; r < RR_ROWS; r += RR_WARPS) {
             const int t = row0 + r;
             if (t < nt)
@@ -208,11 +208,13 @@ router_rows_kernel(const __nv_bfloat16* __restrict__ x1, const __nv_bfloat16* __
     } else if (k <= ROUTER_PICK_SERIAL_K && E * k <= 256) {
         const int t = row0 + (int)threadIdx.x;
         if (threadIdx.x < RR_ROWS && t < nt)
-            router_pick_serial(&part[0][threadIdx.x][0], topk_idx + (size_t)t * k, topk_w + (size_t)t * k, E, k);
+            router_pick_serial(&part[0][threadIdx.x][0], topk_idx + (size_t)t * k, topk_w + (size_t)t * k, E, k,
+                               rule.scored == 2);
     } else {
         for (int r = warp; r < RR_ROWS; r += RR_WARPS) {
             const int t = row0 + r;
-            if (t < nt) router_pick(&part[0][r][0], topk_idx + (size_t)t * k, topk_w + (size_t)t * k, E, k, lane);
+            if (t < nt)
+                router_pick(&part[0][r][0], topk_idx + (size_t)t * k, topk_w + (size_t)t * k, E, k, lane, rule.scored == 2);
         }
     }
     if (!lists.done) return;
@@ -317,7 +319,7 @@ static int router_launch(const void* x1, const void* wr, int* topk_idx, float* t
     if (nt == 0) return 0;
     int warps = E < ROUTER_WARPS ? E : ROUTER_WARPS;
     if (nt >= 1024 && warps > 4) warps = 4;   // many tokens: fewer, longer-lived warps per token
-    TB_LAUNCH((router_kernel<T>), nt, warps * 32, (size_t)E * sizeof(float) * (rule.scored ? 2 : 1), s,
+    TB_LAUNCH((router_kernel<T>), nt, warps * 32, (size_t)E * sizeof(float) * (rule.scored == 1 ? 2 : 1), s,
         (const T*)x1, (const T*)wr, topk_idx, topk_w, logits_out, nt, d, E, k, lists, rule);
     return tb_last_error();
 }
@@ -359,6 +361,37 @@ static int identity_rows_launch(const void* x1, void* y, const int* group_offset
     return tb_last_error();
 }
 
+template <typename T>
+__global__ void __launch_bounds__(128) moe_scaled_rows_kernel(const T* __restrict__ x1, const float* __restrict__ topk_w,
+                                                              const int* __restrict__ pair_row, T* __restrict__ out,
+                                                              int d, int k, int vec) {
+    pdl_sync();
+    const int p = blockIdx.x;
+    const float w = topk_w[p];
+    const T* from = x1 + (size_t)(p / k) * d;
+    T* to = out + (size_t)(pair_row ? pair_row[p] : p) * d;
+    if (vec) {
+        for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+            float v[8];
+            load8(from + c, v);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] *= w;
+            store8(to + c, v);
+        }
+        return;
+    }
+    for (int c = threadIdx.x; c < d; c += blockDim.x) stf(to + c, w * ldf(from + c));
+}
+template <typename T>
+static int scaled_rows_launch(const void* x1, const float* topk_w, const int* pair_row, void* out, int M, int d, int k,
+                              cudaStream_t s) {
+    if (M < 0 || d <= 0 || k <= 0 || !topk_w) return TB_ERR_ARG;
+    if (M == 0) return 0;
+    const int vec = d % 8 == 0 && (((uintptr_t)x1 | (uintptr_t)out) & 15) == 0;
+    TB_LAUNCH((moe_scaled_rows_kernel<T>), M, 128, 0, s, (const T*)x1, topk_w, pair_row, (T*)out, d, k, vec);
+    return tb_last_error();
+}
+
 extern "C" {
 // With `done` (one zeroed word that the kernel leaves zeroed) the dispatch lists of tb_moe_dispatch are built
 // by the same kernel; the three list pointers are then required.
@@ -390,6 +423,33 @@ int tb_router_scored_bf16(const void* x1, const void* wr, const float* bias, int
     return router_launch<__nv_bfloat16>(x1, wr, topk_idx, topk_w, nullptr, nt, d, E, k,
                                         DispatchLists{group_offsets, sorted_token, pair_row, done}, s,
                                         RouterRule{1, bias});
+}
+// The sigmoid rule (see RouterRule): the k largest logits, weights = their sigmoids, not renormalized.
+int tb_router_sigmoid_f32(const void* x1, const void* wr, int* topk_idx, float* topk_w, int* group_offsets,
+                          int* sorted_token, int* pair_row, unsigned* done, int nt, int d, int E, int k,
+                          cudaStream_t s) {
+    if (done && !(group_offsets && sorted_token && pair_row)) return TB_ERR_ARG;
+    return router_launch<float>(x1, wr, topk_idx, topk_w, nullptr, nt, d, E, k,
+                                DispatchLists{group_offsets, sorted_token, pair_row, done}, s, RouterRule{2, nullptr});
+}
+int tb_router_sigmoid_bf16(const void* x1, const void* wr, int* topk_idx, float* topk_w, int* group_offsets,
+                           int* sorted_token, int* pair_row, unsigned* done, int nt, int d, int E, int k,
+                           cudaStream_t s) {
+    if (done && !(group_offsets && sorted_token && pair_row)) return TB_ERR_ARG;
+    return router_launch<__nv_bfloat16>(x1, wr, topk_idx, topk_w, nullptr, nt, d, E, k,
+                                        DispatchLists{group_offsets, sorted_token, pair_row, done}, s,
+                                        RouterRule{2, nullptr});
+}
+// Rows for experts whose weight multiplies what they READ: out[dst(p)] = topk_w[p] * x1[p / k] for every pair
+// p = token * k + choice; dst(p) = pair_row[p] (the pair's place among the rows sorted by expert) or p itself when
+// pair_row is null.  The product is float, one rounding at the store.
+int tb_moe_scaled_rows_f32(const void* x1, const float* topk_w, const int* pair_row, void* out, int M, int d, int k,
+                           cudaStream_t s) {
+    return scaled_rows_launch<float>(x1, topk_w, pair_row, out, M, d, k, s);
+}
+int tb_moe_scaled_rows_bf16(const void* x1, const float* topk_w, const int* pair_row, void* out, int M, int d, int k,
+                            cudaStream_t s) {
+    return scaled_rows_launch<__nv_bfloat16>(x1, topk_w, pair_row, out, M, d, k, s);
 }
 // Experts that hand their input through: the rows of the groups from `first` on receive their token's activations.
 // Sorted rows (group_offsets, sorted_token): rows m >= group_offsets[first], y[m] = x1[sorted_token[m]].
@@ -433,6 +493,13 @@ int tb_router_rows_scored_bf16(const void* x1, const void* wr, const float* bias
     return router_rows_entry(x1, wr, topk_idx, topk_w, nullptr, group_offsets, sorted_token, pair_row, done, nt, d, E, k,
                              RouterRule{1, bias}, s);
 }
+// The same with the sigmoid rule (see tb_router_sigmoid_*).
+int tb_router_rows_sigmoid_bf16(const void* x1, const void* wr, int* topk_idx, float* topk_w, int* group_offsets,
+                                int* sorted_token, int* pair_row, unsigned* done, int nt, int d, int E, int k,
+                                cudaStream_t s) {
+    return router_rows_entry(x1, wr, topk_idx, topk_w, nullptr, group_offsets, sorted_token, pair_row, done, nt, d, E, k,
+                             RouterRule{2, nullptr}, s);
+}
 int tb_moe_dispatch(const int* topk_idx, int* group_offsets, int* sorted_token, int* pair_row, int M, int k, int E,
                     cudaStream_t s) {
     if (M < 0 || k <= 0 || E <= 0) return TB_ERR_ARG;
@@ -458,6 +525,11 @@ TB_TAPE_REGISTER(tb_router_rows_bf16)
 TB_TAPE_REGISTER(tb_router_rows_scored_bf16)
 TB_TAPE_REGISTER(tb_router_scored_f32)
 TB_TAPE_REGISTER(tb_router_scored_bf16)
+TB_TAPE_REGISTER(tb_router_sigmoid_f32)
+TB_TAPE_REGISTER(tb_router_sigmoid_bf16)
+TB_TAPE_REGISTER(tb_router_rows_sigmoid_bf16)
+TB_TAPE_REGISTER(tb_moe_scaled_rows_f32)
+TB_TAPE_REGISTER(tb_moe_scaled_rows_bf16)
 TB_TAPE_REGISTER(tb_moe_identity_rows_f32)
 TB_TAPE_REGISTER(tb_moe_identity_rows_bf16)
 TB_TAPE_REGISTER(tb_moe_dispatch)

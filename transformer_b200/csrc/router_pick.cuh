@@ -6,8 +6,10 @@
 
 // The k largest of lg[0..E) and their softmax weights, by one warp; lg is consumed.  Up to 32 choices stay in
 // registers (choice j in lane j) and leave in one store each; more go through memory.
+// With `sigmoid` the weights are 1 / (1 + exp(-v_j)) of the kept logits as they are (scores of their own, not
+// renormalized); the choice is the same, since the sigmoid keeps the order.
 __device__ __forceinline__ void router_pick(float* lg, int* __restrict__ idx_out, float* __restrict__ w_out, int E, int k,
-                                            int lane) {
+                                            int lane, bool sigmoid = false) {
     float v0 = 0.f, sum = 0.f, my_p = 0.f;
     int my_i = 0;
     const bool in_regs = k <= 32;
@@ -32,7 +34,7 @@ __device__ __forceinline__ void router_pick(float* lg, int* __restrict__ idx_out
         }
         if (bi >= E) bi = 0;   // only when every remaining logit is -inf or NaN
         if (j == 0) v0 = best;
-        const float p = expf(best - v0);
+        const float p = sigmoid ? 1.0f / (1.0f + expf(-best)) : expf(best - v0);
         sum += p;
         if (in_regs) {
             if (lane == j) {
@@ -46,7 +48,7 @@ __device__ __forceinline__ void router_pick(float* lg, int* __restrict__ idx_out
         if (lane == 0) lg[bi] = __int_as_float(0x7fc00000);   // NaN compares false with everything: taken
         __syncwarp();
     }
-    const float inv = 1.0f / sum;
+    const float inv = sigmoid ? 1.0f : 1.0f / sum;
     if (in_regs) {
         if (lane < k) {
             idx_out[lane] = my_i;
@@ -61,7 +63,7 @@ __device__ __forceinline__ void router_pick(float* lg, int* __restrict__ idx_out
 // memory at once, a thread per token costs far fewer instructions than a warp per token.
 #define ROUTER_PICK_SERIAL_K 8
 __device__ __forceinline__ void router_pick_serial(float* lg, int* __restrict__ idx_out, float* __restrict__ w_out, int E,
-                                                   int k) {
+                                                   int k, bool sigmoid = false) {
     float p[ROUTER_PICK_SERIAL_K];
     float v0 = 0.f, sum = 0.f;
 #pragma unroll
@@ -78,12 +80,12 @@ __device__ __forceinline__ void router_pick_serial(float* lg, int* __restrict__ 
         }
         if (bi >= E) bi = 0;
         if (j == 0) v0 = best;
-        p[j] = expf(best - v0);
+        p[j] = sigmoid ? 1.0f / (1.0f + expf(-best)) : expf(best - v0);
         sum += p[j];
         idx_out[j] = bi;
         lg[bi] = __int_as_float(0x7fc00000);
     }
-    const float inv = 1.0f / sum;
+    const float inv = sigmoid ? 1.0f : 1.0f / sum;
 #pragma unroll
     for (int j = 0; j < ROUTER_PICK_SERIAL_K; ++j)
         if (j < k) w_out[j] = p[j] * inv;
@@ -91,6 +93,7 @@ __device__ __forceinline__ void router_pick_serial(float* lg, int* __restrict__ 
 
 // How the logits become a choice.  scored == 0: the k largest logits, softmax over the kept (router_pick).
 // scored == 1: softmax over all outputs, the k largest of score + bias, weights = scores (router_pick_scored).
+// scored == 2: the k largest logits, weights = their sigmoids as they are (router_pick with `sigmoid`).
 struct RouterRule {
     int scored;
     const float* bias;

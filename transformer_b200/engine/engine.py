@@ -41,7 +41,8 @@ def _pending_signature(pending):
     if isinstance(pending, PairDelta):
         return ("p", _pending_signature(pending.first), _pending_signature(pending.second))
     if isinstance(pending, NormedDelta):      # names a weight of the layer before: equal only for the same layer
-        return ("n", _pending_signature(pending.delta), pending.weight.data_ptr(), pending.eps)
+        return ("n", _pending_signature(pending.delta), pending.weight.data_ptr(), pending.eps,
+                0 if pending.bias is None else pending.bias.data_ptr(), pending.center)
     return ("w", pending.rows.data_ptr(), pending.index.data_ptr(), pending.weights.data_ptr(), pending.k,
             tuple(pending.rows.shape))
 

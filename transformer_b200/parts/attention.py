@@ -21,8 +21,14 @@ learned multiplier of every query head's scores (``temperature``, weights ``temp
 by their own position over all of their entries, in adjacent pairs, with the rotary part's base and no rescaling,
 and an output that is turned back by the query's position (``value_rotation``); a mask of chunks (``chunk``:
 position i sees j <= i iff i // chunk == j // chunk); a learned number per head that joins the softmax's
-denominator (``sink``, weights ``sink``).  With any of these the kernel between the product and the attention is
-``tb_head_prep`` (csrc/head_prep.cu): convolution, norms, temperature, both rotations and the cache write at once.
+denominator (``sink``, weights ``sink``); values blended with those that an earlier layer made for the same token
+(``value_mix``: the layer that says "source" leaves its values, as they are after the convolution and before any
+rotation, in float scratch memory of the step; a layer that says "blend" caches (1 - l) v + l v_source with its own
+learned number l, weights ``vmix``).  With any of these the kernel between the product and the attention is
+``tb_head_prep`` (csrc/head_prep.cu): convolution, norms, temperature, the blend, both rotations and the cache write
+at once.  That kernel turns adjacent pairs; a rotary part that pairs entry i with i + dims/2 is met by reordering,
+once at binding, the rows of the query and key projections (and of their norm weights and convolutions) that make the
+rotated entries: a permutation applied to queries and keys alike, which leaves every score as it was.
 """
 from __future__ import annotations
 
@@ -74,10 +80,14 @@ class Attention(Mixer):
         self.value_rotation = bool(params.get("value_rotation", False))
         self.chunk = int(params.get("chunk") or 0)
         self.sink = bool(params.get("sink", False))
+        self.value_mix = params.get("value_mix")
+        if self.value_mix not in (None, "source", "blend"):
+            raise ValueError(f"value_mix is 'source', 'blend' or absent, got {self.value_mix!r}")
         if self.conv_taps < 0 or self.conv_taps > 16 or self.chunk < 0:
             raise ValueError("convolutions of 1 to 16 taps; chunk not negative")
         # the second family of mechanisms: its own kernel between the product and the attention
-        self.prepared = bool(self.conv_taps or self.qk_norm == "head" or self.temperature or self.value_rotation)
+        self.prepared = bool(self.conv_taps or self.qk_norm == "head" or self.temperature or self.value_rotation or
+                             self.value_mix)
         if self.prepared and (self.gate or self.qk_norm == "whole"):
             raise ValueError("a norm over the whole projection or an output gate does not go with the per-head family")
         if self.dv <= 0 or self.dv > 256 or self.window < 0 or self.keep_first < 0 or self.softcap < 0:
@@ -140,6 +150,8 @@ class Attention(Mixer):
             decl["temp"] = ParamDecl((self.nh,), "norm", "ones")
         if self.sink:
             decl["sink"] = ParamDecl((self.nh,), "norm", "normal")
+        if self.value_mix:      # the source has the number too and does not use it
+            decl["vmix"] = ParamDecl((), "norm", "normal")
         if self.position is not None:      # what the position encoding has learned travels with its mixer
             decl.update({"position." + n: d for n, d in self.position.parameters().items()})
         return decl
@@ -148,6 +160,23 @@ class Attention(Mixer):
         super().bind(tensors)
         if self.position is not None:
             self.position.bind({n: tensors["position." + n] for n in self.position.parameters()})
+        if "vmix" in self.weights:
+            self.weights["vmix"] = self.weights["vmix"].float().reshape(1).contiguous()
+        if self.prepared and self.rdims and self.position.rotation()[2]:
+            # halves paired: entry i of the rotated part goes to 2i, entry i + rdims/2 to 2i + 1, in every query and
+            # key head, so that the kernel's adjacent pairs are the design's pairs
+            r = self.rdims
+            order = [j for i in range(r // 2) for j in (i, i + r // 2)] + list(range(r, self.dh))
+            rows = [h * self.dh + j for h in range(self.nh + self.nkvh) for j in order]
+            rows += list(range(len(rows), self.qkv_width))
+            at = torch.tensor(rows, device=self.weights["wqkv"].device)
+            self.weights["wqkv"] = self.weights["wqkv"][at].contiguous()
+            if "conv" in self.weights:
+                self.weights["conv"] = self.weights["conv"][at].contiguous()
+            if self.qk_norm == "head":
+                one = torch.tensor(order, device=self.weights["q_norm"].device)
+                self.weights["q_norm"] = self.weights["q_norm"][one].contiguous()
+                self.weights["k_norm"] = self.weights["k_norm"][one].contiguous()
 
     def cache_need(self):
         if self.dv != self.dh:
@@ -169,19 +198,20 @@ class Attention(Mixer):
         table = ctx.page_table(cache)
         cos = sin = vcos = vsin = None
         if self.rdims:
-            cos, sin, half = self.position.rotation()
-            if half:
-                raise ValueError("the per-head family rotates adjacent pairs")
+            cos, sin, _ = self.position.rotation()      # halves paired: the rows were reordered at binding
         if self.value_position is not None:
             vcos, vsin, _ = self.value_position.rotation()
         kc, vc = (cache.k, cache.v) if cache.writable else (None, None)
         q = ctx.scratch("attn.q", (nt, self.nh * self.dh), self.dtype)
+        # the values of the blend's source: written by the source's run, read by the later runs of the same step
+        vfirst = ctx.scratch("attn.v_source", (nt, self.nkvh * self.dv), torch.float32) if self.value_mix else None
         lib.call("tb_head_prep_" + sfx, lib.ptr(z), self.qkv_width, lib.ptr(w.get("conv")), lib.ptr(state),
                  0 if state is None else state.stride(0), lib.ptr(w.get("q_norm")), lib.ptr(w.get("k_norm")),
                  lib.ptr(w.get("temp")), self.eps, lib.ptr(cos), lib.ptr(sin), lib.ptr(vcos), lib.ptr(vsin), lib.ptr(q),
                  lib.ptr(kc), lib.ptr(vc), lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(ctx.seq_start),
                  lib.ptr(ctx.slots), lib.ptr(table), ctx.max_pages, nt, self.nh, self.nkvh, self.dh, self.dv,
-                 self.rdims, max(self.conv_taps, 1), 1 if ctx.decode else 0)
+                 self.rdims, max(self.conv_taps, 1), 1 if ctx.decode else 0, lib.ptr(vfirst),
+                 lib.ptr(w["vmix"]) if self.value_mix == "blend" else 0)
         if self.conv_taps > 1 and not ctx.decode:
             # every token has read the old inputs: the state moves on to the step's last rows
             lib.call("tb_conv_roll_" + sfx, lib.ptr(z), self.qkv_width, lib.ptr(state), state.stride(0),

@@ -103,10 +103,13 @@ class NormedDelta:
     """A part's output that still has to be normed before it joins the stream:  x += delta / rms(delta) * weight
     (a block that norms its parts' outputs as well as their inputs).  ``delta`` is a tensor [nt, d] or a
     :class:`WeightedRows`.  A norm that sets ``takes_normed_delta`` does that norm, the sum and its own norm in one
-    kernel; for any other norm the block applies it to the stream first (:func:`parts.block.resolve`)."""
+    kernel; for any other norm the block applies it to the stream first (:func:`parts.block.resolve`).
+    With ``center`` the norm is a layer norm: x += (delta - mean) / sqrt(var(delta) + eps) * weight + bias."""
     delta: Any
     weight: torch.Tensor      # float [d]
     eps: float
+    bias: Optional[torch.Tensor] = None     # float [d]
+    center: bool = False
 
 
 class Part:

@@ -70,6 +70,32 @@ class DenseSwiGLU(FeedForward):
         matmul_nt(h, self.weights["wd"], out)
 
 
+@FEED_FORWARDS.register("mlp")
+class DenseMLP(FeedForward):
+    """params: width, di, act ("relu2").  A feed-forward without a gate: out = act(x1 Wu^T) Wd^T, with
+    relu2(z) = max(z, 0)^2 (float, one rounding) applied to the first product's result in place."""
+    graph_safe = True
+    launches_only = True
+
+    def __init__(self, params, dtype, device):
+        super().__init__(params, dtype, device)
+        self.d = int(params["width"])
+        self.di = int(params["di"])
+        self.act = params.get("act", "relu2")
+        if self.act != "relu2":
+            raise ValueError(f"unknown activation {self.act!r}; this part has 'relu2'")
+
+    def parameters(self):
+        return {"wu": ParamDecl((self.di, self.d)), "wd": ParamDecl((self.d, self.di))}
+
+    def forward(self, ctx, x1, out) -> None:
+        nt = x1.shape[0]
+        h = ctx.scratch("ff.h", (nt, self.di), self.dtype)
+        matmul_nt(x1, self.weights["wu"], h)
+        lib.call("tb_relu2_" + lib.suffix(self.dtype), lib.ptr(h), nt * self.di)
+        matmul_nt(h, self.weights["wd"], out)
+
+
 @FEED_FORWARDS.register("moe")
 class MoE(FeedForward):
     """params: width, di, nexp, nexp_use; optional: scoring, correction, identity, glu_alpha, glu_limit.
@@ -85,7 +111,12 @@ class MoE(FeedForward):
     * ``identity`` = n: the router has nexp + n outputs, and the last n stand for experts without weights whose
       output is their input.
     * ``glu_limit`` (with ``glu_alpha``): the expert's pair becomes g' * sigmoid(alpha g') * (u' + 1) with
-      g' = min(g, limit), u' = clamp(u, -limit, limit), instead of silu(g) * u."""
+      g' = min(g, limit), u' = clamp(u, -limit, limit), instead of silu(g) * u.
+    * ``scoring`` = "sigmoid": scores = sigmoid(logit), each by itself; the nexp_use largest are chosen (equal values
+      to the lower index); the weights are the chosen scores as they are.
+    * ``weight_on`` = "input": the weight multiplies what the expert reads, out = sum_e expert_e(w_e x1), instead of
+      what it returns.  Every (token, choice) pair gets its own scaled copy of the token's row (one kernel, which
+      also puts the rows in the experts' order), the experts run on those, and their results are summed unweighted."""
     graph_safe = True
     launches_only = True
 
@@ -102,8 +133,13 @@ class MoE(FeedForward):
         if self.R > 1024:
             raise ValueError(f"the routing kernels take up to 1024 experts, got {self.R}")
         self.scoring = params.get("scoring", "kept")
-        if self.scoring not in ("kept", "all"):
+        if self.scoring not in ("kept", "all", "sigmoid"):
             raise ValueError(f"unknown router scoring {self.scoring!r}")
+        self.weight_on = params.get("weight_on", "output")
+        if self.weight_on not in ("output", "input"):
+            raise ValueError(f"the router's weight multiplies the expert's 'output' or 'input', got {self.weight_on!r}")
+        if self.weight_on == "input" and self.identity:
+            raise ValueError("pass-through experts and weights on the input are not combined")
         self.correction = bool(params.get("correction", False))
         if self.correction and self.scoring != "all":
             raise ValueError("a correction of the choice goes with scoring 'all'")
@@ -145,6 +181,19 @@ class MoE(FeedForward):
                      lib.ptr(self.weights.get("correction")), lib.ptr(idx), lib.ptr(w), lib.ptr(offsets),
                      lib.ptr(sorted_token), lib.ptr(pair_row), lib.ptr(done), nt, self.d, self.R, self.k)
             return idx, w, lists is not None
+        if self.scoring == "sigmoid":
+            # the same kernels with another rule for the weights; the block that finishes last builds the lists
+            done = ctx.scratch("moe.done", (1,), torch.int32, zero=True) if lists is not None else None
+            offsets, sorted_token, pair_row = lists if lists is not None else (None, None, None)
+            if self.dtype == torch.bfloat16 and nt > ROUTER_ROWS_FROM and self.R <= 64 and \
+                    lib.try_call("tb_router_rows_sigmoid_bf16", lib.ptr(x1), lib.ptr(self.weights["router"]),
+                                 lib.ptr(idx), lib.ptr(w), lib.ptr(offsets), lib.ptr(sorted_token), lib.ptr(pair_row),
+                                 lib.ptr(done), nt, self.d, self.R, self.k):
+                return idx, w, lists is not None
+            lib.call("tb_router_sigmoid_" + lib.suffix(self.dtype), lib.ptr(x1), lib.ptr(self.weights["router"]),
+                     lib.ptr(idx), lib.ptr(w), lib.ptr(offsets), lib.ptr(sorted_token), lib.ptr(pair_row),
+                     lib.ptr(done), nt, self.d, self.R, self.k)
+            return idx, w, lists is not None
         if self.dtype == torch.bfloat16 and nt > ROUTER_ROWS_FROM and self.R <= 64:
             # many tokens, few experts: 16 tokens' logits are a tensor-core tile, the activations are read once, and
             # the block that finishes last builds the dispatch lists
@@ -165,7 +214,7 @@ class MoE(FeedForward):
 
     def norm_tail(self, ctx, nt):
         """For a few tokens the router rides along with the norm before this part."""
-        if nt > ROUTER_TAIL_ROWS:
+        if nt > ROUTER_TAIL_ROWS or self.scoring == "sigmoid":
             return None
         return NormTail("router", weights=self.weights["router"], k=self.k,
                         index=ctx.scratch("moe.topk_idx", (nt, self.k), torch.int32),
@@ -183,8 +232,13 @@ class MoE(FeedForward):
             h = ctx.scratch("moe.h", (M, self.di), self.dtype)
             y = ctx.scratch("moe.y", (M, self.d), self.dtype)
             pairs = idx.view(-1)
-            if gemm_skinny(x1, self.weights["wgu"], h, groups=self.E, out_kind=2, max_group_rows=nt, row_group=pairs,
-                           x_div=self.k, glu=self.glu) and \
+            src, x_div = x1, self.k
+            if self.weight_on == "input":       # a scaled copy of the token's row for each of its pairs
+                src, x_div = ctx.scratch("moe.scaled_rows", (M, self.d), self.dtype), 1
+                lib.call("tb_moe_scaled_rows_" + sfx, lib.ptr(x1), lib.ptr(w), 0, lib.ptr(src), M, self.d, self.k)
+                w = _ones(nt, self.k, x1.device)
+            if gemm_skinny(src, self.weights["wgu"], h, groups=self.E, out_kind=2, max_group_rows=nt, row_group=pairs,
+                           x_div=x_div, glu=self.glu) and \
                     gemm_skinny(h, self.weights["wd"], y, groups=self.E, max_group_rows=nt, row_group=pairs):
                 ctx.record("moe.topk_idx", idx)
                 if self.identity:       # pairs that chose an expert without weights: the token's own row
@@ -203,8 +257,17 @@ class MoE(FeedForward):
             lib.call("tb_moe_dispatch", lib.ptr(idx), lib.ptr(offsets), lib.ptr(sorted_token), lib.ptr(pair_row),
                      M, self.k, self.R)
         h = ctx.scratch("moe.h", (M, self.di), self.dtype)
-        grouped_matmul(x1, self.weights["wgu"], h, a_rows=sorted_token, group_offsets=offsets, groups=self.E,
-                       swiglu=True, max_group_rows=nt, scratch=ctx.scratch, glu=self.glu)
+        if self.weight_on == "input":
+            # the pairs' scaled rows, already in the experts' order (what the gather before the product does else)
+            src = ctx.scratch("grouped.sorted_rows", (M, self.d), self.dtype)
+            lib.call("tb_moe_scaled_rows_" + sfx, lib.ptr(x1), lib.ptr(w), lib.ptr(pair_row), lib.ptr(src), M, self.d,
+                     self.k)
+            w = _ones(nt, self.k, x1.device)
+            grouped_matmul(src, self.weights["wgu"], h, group_offsets=offsets, groups=self.E, swiglu=True,
+                           max_group_rows=nt, scratch=ctx.scratch, glu=self.glu)
+        else:
+            grouped_matmul(x1, self.weights["wgu"], h, a_rows=sorted_token, group_offsets=offsets, groups=self.E,
+                           swiglu=True, max_group_rows=nt, scratch=ctx.scratch, glu=self.glu)
         y = ctx.scratch("moe.y", (M, self.d), self.dtype)
         grouped_matmul(h, self.weights["wd"], y, group_offsets=offsets, groups=self.E, max_group_rows=nt)
         if self.identity:               # the rows after the last real expert's: their tokens' own rows
@@ -223,6 +286,17 @@ def _identity_rows(n: int, device) -> torch.Tensor:
     if key not in _IDENTITY_ROWS:
         _IDENTITY_ROWS[key] = torch.arange(n, dtype=torch.int32, device=device)
     return _IDENTITY_ROWS[key]
+
+
+_ONES = {}
+
+
+def _ones(nt: int, k: int, device) -> torch.Tensor:
+    """[nt, k] float ones, made once per size: the weights of a sum whose terms were weighted on the way in."""
+    key = (nt, k, str(device))
+    if key not in _ONES:
+        _ONES[key] = torch.ones((nt, k), dtype=torch.float32, device=device)
+    return _ONES[key]
 
 
 def sum_weighted_rows(wr: WeightedRows, out) -> None:

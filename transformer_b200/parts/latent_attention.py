@@ -16,7 +16,10 @@ Variants by parameter: ``q_rank`` 0: the queries come straight from one projecti
 no query norm; Wq rides in the merged first product); ``window`` 0: plain causal attention; a rotary part with
 adjacent pairs (2i, 2i + 1): the kernels pair entry i with i + dims/2, so the rows of the projections that make
 the rotated entries are reordered once at binding (evens, then odds) -- a permutation applied to queries and
-keys alike, which leaves every score as it was.
+keys alike, which leaves every score as it was; ``sink``: a learned number per head (weights ``sink``) that joins
+the softmax's denominator once, with no key and no value; ``head_gate``: head h's output is multiplied by
+sigmoid(Wg x1)_h, one number per head, whose projection (weights ``wg`` [heads, width]) rides in the merged first
+product, behind the latent's rows.
 """
 from __future__ import annotations
 
@@ -44,6 +47,8 @@ class LatentAttention(Mixer):
         self.rank, self.q_rank, self.window = g("kv_rank"), g("q_rank"), g("window")
         self.scale, self.eps = float(params["scale"]), float(params["eps"])
         self.own_latent = bool(params.get("own_latent", True))
+        self.sink = bool(params.get("sink", False))
+        self.head_gate = bool(params.get("head_gate", False))
         pos = params.get("position")
         if not isinstance(pos, PartSpec):
             raise ValueError("latent attention needs the rotary encoding of its rotated part ('position')")
@@ -85,6 +90,10 @@ class LatentAttention(Mixer):
             decl["uq"] = ParamDecl((self.H * self.q_head, self.q_rank))
         if self.own_latent:
             decl["c_norm"] = ParamDecl((self.rank,), "norm", "ones")
+        if self.sink:
+            decl["sink"] = ParamDecl((self.H,), "norm", "normal")
+        if self.head_gate:
+            decl["wg"] = ParamDecl((self.H, self.d))
         return decl
 
     def _halves(self, rows: torch.Tensor) -> torch.Tensor:
@@ -109,6 +118,13 @@ class LatentAttention(Mixer):
                 wd[-self.rot:] = self._halves(wd[-self.rot:].clone())
                 self.weights["wdown"] = wd
             self.weights[qname] = wq
+        if self.head_gate:
+            # the gates' rows join the first product, behind everything else, so that they cost no launch of their
+            # own; zero rows up to a multiple of eight keep the rows of its result 16-byte aligned
+            wd, wg = self.weights["wdown"], self.weights.pop("wg")
+            self.gate_at = wd.shape[0]
+            pad = (-(wd.shape[0] + self.H)) % 8
+            self.weights["wdown"] = torch.cat([wd, wg, wd.new_zeros((pad, self.d))], dim=0).contiguous()
 
     def cache_need(self):
         return CacheNeed("latent", 1, self.rank + self.rot, (("rank", self.rank), ("rot", self.rot)))
@@ -139,6 +155,8 @@ class LatentAttention(Mixer):
                          self.eps, 0, lib.ptr(cache.kv), lib.ptr(ctx.tok_seq), lib.ptr(ctx.tok_pos), lib.ptr(table),
                          ctx.max_pages, lib.ptr(cos), lib.ptr(sin), nt, 0, self.rank, self.rot, self.rdims)
         ldq = q.stride(0)
+        sinks = w.get("sink")
+        gate = a[:, self.gate_at:] if self.head_gate else None
         qa = ctx.scratch("latent.qa", (nt, H, self.rank), self.dtype)
         batched_matmul(q.as_strided((nt, H, self.dim), (ldq, self.q_head, 1)), w["ukT"], qa)
         ol = ctx.scratch("latent.ol", (nt, H, self.rank), self.dtype)
@@ -155,12 +173,12 @@ class LatentAttention(Mixer):
                                 lib.ptr(cache.kv), lib.ptr(tiles.seq), lib.ptr(tiles.t0), lib.ptr(tiles.nq),
                                 lib.ptr(ctx.tok_pos), lib.ptr(table), lib.ptr(cos), lib.ptr(sin), tiles.count, nt,
                                 ctx.max_pages, ldq, self.q_head, H, self.rank, self.rot, self.rdims,
-                                self.window, splits, self.scale)
+                                self.window, splits, self.scale, lib.ptr(sinks), lib.ptr(gate), wa)
         if not done:
             lib.call("tb_latent_attention_" + sfx, lib.ptr(qa), lib.ptr(q), lib.ptr(ol), lib.ptr(cache.kv),
                      lib.ptr(tiles.seq), lib.ptr(tiles.t0), lib.ptr(tiles.nq), lib.ptr(ctx.tok_pos), lib.ptr(table),
                      lib.ptr(cos), lib.ptr(sin), tiles.count, ctx.max_pages, ldq, self.q_head, self.dim, H,
-                     self.rank, self.rot, self.rdims, self.window, self.scale)
+                     self.rank, self.rot, self.rdims, self.window, self.scale, lib.ptr(sinks), lib.ptr(gate), wa)
         o = ctx.scratch("latent.o", (nt, H, self.vdim), self.dtype)
         batched_matmul(ol, w["uv"].view(H, self.vdim, self.rank), o)
         matmul_nt(o.view(nt, H * self.vdim), w["wo"], out)

@@ -71,5 +71,5 @@ class MatrixMemory(Mixer):
         y = ctx.scratch("mlstm.y", (nt, H * self.vdim), self.dtype)
         g = z[:, 2 * H * self.dim + H * self.vdim:]
         lib.call("tb_mlstm_out_" + sfx, lib.ptr(o), lib.ptr(g), self.z_width, lib.ptr(w["norm"]), lib.ptr(y), nt, H,
-                 self.vdim, self.eps)
+                 self.vdim, self.eps, 0)
         matmul_nt(y, w["wo"], out)

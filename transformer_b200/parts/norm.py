@@ -1,4 +1,5 @@
-"""RMSNorm fused with the residual sum (models/llama/common/src/compute.rs:207,275,362)."""
+"""RMSNorm fused with the residual sum (models/llama/common/src/compute.rs:207,275,362); a layer norm (mean taken
+off, weight and bias, an optional multiplier per channel) with the same fusions; and no norm at all."""
 from __future__ import annotations
 
 from ..csrc import lib
@@ -82,6 +83,53 @@ class RMSNorm(Norm):
                  self.width, lib.ptr(warm), 0 if warm is None else warm.numel() * warm.element_size())
 
 
+@NORMS.register("layernorm")
+class LayerNorm(Norm):
+    """params: width, eps, bias (default True), scale (default False).  y = (v - mean v) / sqrt(var v + eps) * weight
+    + bias, the variance being the mean of the squared deviations.  With ``scale`` the result is multiplied channel
+    by channel by a further learned vector ("scale": a block's layer scale), which is folded into the bound weight
+    and bias (float, once).  Statistics and the residual sum are float; one rounding at the store.  A pending
+    :class:`NormedDelta` of either kind is normed, added and normed again in the same kernel."""
+    graph_safe = True
+    launches_only = True
+    takes_weighted_rows = True
+    takes_normed_delta = True
+
+    def __init__(self, params, dtype, device):
+        super().__init__(params, dtype, device)
+        self.width = int(params["width"])
+        self.eps = float(params["eps"])
+        self.bias = bool(params.get("bias", True))
+        self.scale = bool(params.get("scale", False))
+
+    def parameters(self):
+        decl = {"weight": ParamDecl((self.width,), "norm", "ones")}
+        if self.bias:
+            decl["bias"] = ParamDecl((self.width,), "norm", "normal")
+        if self.scale:
+            decl["scale"] = ParamDecl((self.width,), "norm", "ones")
+        return decl
+
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        if self.scale:
+            s = self.weights.pop("scale").float()
+            self.weights["weight"] = (self.weights["weight"].float() * s).contiguous()
+            if self.bias:
+                self.weights["bias"] = (self.weights["bias"].float() * s).contiguous()
+
+    def as_normed(self, delta) -> NormedDelta:
+        """``delta`` as something that this norm is still to be applied to before it joins the stream."""
+        return NormedDelta(delta, self.weights["weight"], self.eps, self.weights.get("bias"), True)
+
+    def forward(self, ctx, x, delta, rows, y) -> None:
+        post = None
+        if isinstance(delta, NormedDelta):
+            post, delta = delta, delta.delta
+        post_add_layernorm(self.dtype, x, delta, post, rows, self.weights["weight"], self.weights.get("bias"), self.eps,
+                           True, y)
+
+
 @NORMS.register("none")
 class NoNorm(Norm):
     """params: width.  No norm at all, for blocks whose parts read the residual stream as it is: the pending
@@ -126,6 +174,11 @@ def _route(sfx, y, tail, n_out, width) -> None:
 def post_add_rmsnorm(dtype, x, pending: NormedDelta, rows, weight, eps, y, tail=None) -> None:
     """x[rows] += pending.delta / rms(pending.delta) * pending.weight (written back when ``rows`` is None), then
     y = x / rms(x) * weight; with ``y`` None only the sum.  ``tail``: a "router" NormTail computed along the way."""
+    if pending.center or pending.bias is not None:
+        post_add_layernorm(dtype, x, pending.delta, pending, rows, weight, None, eps, False, y)
+        if tail is not None:
+            _route(lib.suffix(dtype), y, tail, y.shape[0], x.shape[1])
+        return
     delta, wy, idx, wts, k = pending.delta, None, None, None, 0
     if isinstance(delta, WeightedRows):
         wy, idx, wts, k, delta = delta.rows, delta.index, delta.weights, delta.k, None
@@ -142,6 +195,24 @@ def post_add_rmsnorm(dtype, x, pending: NormedDelta, rows, weight, eps, y, tail=
              lib.ptr(y), n_out, x.shape[1])
     if tail is not None:
         _route(sfx, y, tail, n_out, x.shape[1])
+
+
+def post_add_layernorm(dtype, x, delta, post, rows, weight, bias, eps, center, y) -> None:
+    """x[rows] += N_post(delta) (written back when ``rows`` is None), then y = N(x[rows]; weight, bias, eps, center).
+    ``delta``: a tensor, a :class:`WeightedRows` or None; ``post``: the :class:`NormedDelta` whose norm the delta
+    still has to pass (None: it joins as it is); ``weight`` None: y is the sum itself; ``y`` None: only the sum."""
+    wy = idx = wts = None
+    k = 0
+    if isinstance(delta, WeightedRows):
+        wy, idx, wts, k, delta = delta.rows, delta.index, delta.weights, delta.k, None
+    n_out = x.shape[0] if y is None else y.shape[0]
+    pw = pb = None
+    pe, pc = 0.0, 0
+    if post is not None:
+        pw, pb, pe, pc = post.weight, post.bias, float(post.eps), 1 if post.center else 0
+    lib.call("tb_post_add_layernorm_" + lib.suffix(dtype), lib.ptr(x), lib.ptr(delta), lib.ptr(wy), lib.ptr(idx),
+             lib.ptr(wts), k, lib.ptr(pw), lib.ptr(pb), pe, pc, lib.ptr(rows), lib.ptr(weight), lib.ptr(bias), float(eps),
+             1 if center else 0, lib.ptr(y), n_out, x.shape[1])
 
 
 def pair_add_rmsnorm(dtype, x, pending, rows, w1, y1, w2, y2, eps) -> None:

@@ -19,7 +19,7 @@ _TABLES = {}
 
 @POSITIONS.register("rope")
 class Rope(Position):
-    """params: dh, theta, pairing ("adjacent" | "half"), positions (table length), scaling (optional).
+    """params: dh, theta, pairing ("adjacent" | "half"), positions (table length); optional: scaling, ramp, linear.
 
     ``scaling`` = (factor, low, high, original) rescales the frequencies by wavelength l = 2 pi / f against a context
     of ``original`` tokens: f stays where l < original / high, becomes f / factor where l > original / low, and
@@ -28,7 +28,10 @@ class Rope(Position):
     ``ramp`` = (factor, original, fast, slow) rescales them by their index instead: with
     n(t) = dh ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(n(fast)), 0), hi = min(ceil(n(slow)), dh - 1) and
     r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency is f_i / factor * r_i + f_i (1 - r_i), and cos
-    and sin are both multiplied by 0.1 ln(factor) + 1."""
+    and sin are both multiplied by 0.1 ln(factor) + 1.
+
+    ``linear`` = factor divides every frequency by the same number (positions stretched by it); it may stand beside
+    either of the other two and is applied first."""
     graph_safe = True
     launches_only = True
 
@@ -46,6 +49,9 @@ class Rope(Position):
         self.ramp = None if rp is None else tuple(float(v) for v in rp)
         if self.ramp is not None and (len(self.ramp) != 4 or self.scaling is not None):
             raise ValueError(f"rope ramp is (factor, original, fast, slow) and excludes 'scaling', got {rp!r}")
+        self.linear = float(params.get("linear") or 1.0)
+        if not self.linear > 0:
+            raise ValueError(f"a linear rescaling divides by a positive factor, got {self.linear}")
         if self.dh % 2:
             raise ValueError(f"rotary pairs need an even head size, got {self.dh}")
         if self.pairing not in ("adjacent", "half"):
@@ -60,10 +66,10 @@ class Rope(Position):
         return cos, sin, self.half_pairing
 
     def tables(self):
-        key = (self.dh, self.theta, self.positions, self.scaling, self.ramp, str(self.device))
+        key = (self.dh, self.theta, self.positions, self.scaling, self.ramp, self.linear, str(self.device))
         if key not in _TABLES:
             i = torch.arange(self.dh // 2, dtype=torch.float64)
-            inv_freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / self.dh)
+            inv_freq = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / self.dh) / self.linear
             if self.scaling is not None:
                 factor, low, high, original = self.scaling
                 turns = original * inv_freq / (2.0 * torch.pi)          # original / wavelength
