@@ -237,10 +237,11 @@ def sub(tensors: Dict[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tensor
 
 
 def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens: Sequence[int], store=None, layers_out=None,
-            choices=None) -> torch.Tensor:
+            choices=None, scores_out=None) -> torch.Tensor:
     """Logits [n, vocab] of one sequence from its first token.  ``layers_out``: a list that receives the stream
     after every layer.  ``choices``: per layer with experts, (experts, weights or None) to use instead of the
-    router's own pick (weights None: the router's scores of the given experts)."""
+    router's own pick (weights None: the router's scores of the given experts).  ``scores_out``: a dict that
+    receives every such layer's router scores [n, experts]."""
     eps = cfg["norm"]["eps"]
     x = tensors["embed"][torch.as_tensor(list(tokens), dtype=torch.long)]
     v_first = None
@@ -269,6 +270,8 @@ def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens: Sequence[int], 
                 y = dense_ff(h, wf, store)
             elif f["kind"] == "moe":
                 choice = None
+                if scores_out is not None:
+                    scores_out[i] = torch.sigmoid(h @ wf["router"].T)
                 if choices is not None and i in choices:
                     experts, weights = choices[i]
                     if weights is None:

@@ -534,7 +534,7 @@ def test_convolution_head_norms_rotations_and_cache_write(dtype, nh, nkvh, dk, d
         lib.call("tb_head_prep_" + lib.suffix(td), lib.ptr(dz), C, lib.ptr(d_conv) if taps else 0, lib.ptr(state),
                  state.stride(0), lib.ptr(d_wq), lib.ptr(d_wk), lib.ptr(d_temp), 1e-5, lib.ptr(d_cos), lib.ptr(d_sin),
                  lib.ptr(d_vcos), lib.ptr(d_vsin), lib.ptr(q), lib.ptr(kc), lib.ptr(vc), lib.ptr(d_seq), lib.ptr(d_pos),
-                 lib.ptr(d_start), lib.ptr(d_slots), lib.ptr(d_table), 3, nt, nh, nkvh, dk, dv, rdims, max(taps, 1), 0)
+                 lib.ptr(d_start), lib.ptr(d_slots), lib.ptr(d_table), 3, nt, nh, nkvh, dk, dv, rdims, max(taps, 1), 0, 0, 0)
         if taps > 1:
             lib.call("tb_conv_roll_" + lib.suffix(td), lib.ptr(dz), C, lib.ptr(state), state.stride(0), lib.ptr(d_start),
                      lib.ptr(d_slots), len(lens), C, taps)

@@ -258,12 +258,12 @@ def _latent_attention(dtype, H, rank, rot, window, lens_before, lens_new, q_of, 
         lib.call("tb_latent_attention_mma_bf16", lib.ptr(d_qa), lib.ptr(d_q), lib.ptr(out), lib.ptr(partial),
                  lib.ptr(d_cache), lib.ptr(d_seq), lib.ptr(d_t0), lib.ptr(d_nq), lib.ptr(d_pos), lib.ptr(d_table),
                  lib.ptr(ones), lib.ptr(zeros), len(tile_seq), nt, max_pages, H * (4 + rot), 4 + rot, H, rank, rot, rot,
-                 window, splits, scale)
+                 window, splits, scale, 0, 0, 0)
     else:
         lib.call("tb_latent_attention_" + ("f32" if dtype == "float32" else "bf16"), lib.ptr(d_qa), lib.ptr(d_q),
                  lib.ptr(out), lib.ptr(d_cache), lib.ptr(d_seq), lib.ptr(d_t0), lib.ptr(d_nq), lib.ptr(d_pos),
                  lib.ptr(d_table), lib.ptr(ones), lib.ptr(zeros), len(tile_seq), max_pages, H * (4 + rot), 4 + rot, 4, H,
-                 rank, rot, rot, window, scale)
+                 rank, rot, rot, window, scale, 0, 0, 0)
     torch.cuda.synchronize()
     from transformer_b200.csrc.lib import gemm_tc_status
     assert gemm_tc_status() == 0
