@@ -4,6 +4,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --design salepel [--sizes s,m]      another design beside Llama-MoE at equal sizes (see bench_design)
     python bench.py --design zufadra [--sizes s,m]      the Zufadra design beside a dense Llama at equal sizes
+    python bench.py --design fugavik [--sizes s,m]      the Fugavik design beside Zufadra, Dumalix and Llama-MoE
 
 The default run has the layer sizes of the LLaMA-MoE-3.5B (4/16) shape (32 layers, width 4096,
 32/32 heads of 128, 16 experts top-4 of width 688, vocabulary 32000, context 4096) with random
@@ -228,6 +229,30 @@ def dumalix_shapes(size):
     return dumalix, zufadra, design_shapes(size)[0]
 
 
+def fugavik_shapes(size):
+    """(Fugavik config, Zufadra config, Dumalix config, Llama-MoE config) for a named size.  The Fugavik layers go
+    delta rule, attention, attention, latent attention, twice; the feed-forwards alternate between the dense pair and
+    the experts.  Zufadra (delta rule, attention over the paged cache with a gate or a sink in the same kernels, blocks
+    that norm what their parts produce, dense feed-forward) is the closest model for the delta rule, the attention, the
+    norms and the dense products; Dumalix has the latent attention of the same kind (queries from one projection, plain
+    causal); Llama-MoE the experts of the same sizes."""
+    d, L, H, G, dim, lat_dim, rank, ff, E, top, eff = {
+        "s": (1024, 8, 8, 2, 128, 64, 256, 2816, 8, 2, 512),
+        "m": (2048, 8, 16, 4, 128, 128, 512, 5632, 16, 4, 704),
+    }[size]
+    att = {"heads": H, "kv_heads": G, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "v_mix": True,
+           "rot": {"base": 500000.0, "dims": dim, "scaling": {"factor": 4.0}}}
+    lat = {"heads": H, "dim": lat_dim, "vdim": lat_dim, "kv_rank": rank, "scale": lat_dim ** -0.5}
+    mem = {"heads": H, "kv_heads": H, "dim": dim, "vdim": dim, "conv": 4}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "top": top}}
+    kinds = [("delta", mem), ("attention", att), ("attention", att), ("latent_attention", lat)]
+    layers = [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": dense if i % 2 == 0 else moe} for i in range(L)]
+    fugavik = {"architecture": "Fugavik", "vocab": 32000, "width": d, "norm": {"eps": 1e-6}, "max_context": 8192,
+               "layers": layers}
+    return fugavik, zufadra_shapes(size)[0], dumalix_shapes(size)[0], design_shapes(size)[1]
+
+
 def bench_design(args):
     """Prefill and decode throughput of another design beside the closest existing model of equal sizes, and the
     device time of every kernel family in one eager step of each (CUDA events around each launch).  One JSON line."""
@@ -241,7 +266,8 @@ def bench_design(args):
     gen = torch.Generator().manual_seed(7)
     names, shapes = {"salepel": (("salepel", "llama_moe"), design_shapes),
                      "zufadra": (("zufadra", "llama_dense"), zufadra_shapes),
-                     "dumalix": (("dumalix", "zufadra_attention", "salepel"), dumalix_shapes)}[args.design]
+                     "dumalix": (("dumalix", "zufadra_attention", "salepel"), dumalix_shapes),
+                     "fugavik": (("fugavik", "zufadra", "dumalix", "llama_moe"), fugavik_shapes)}[args.design]
     out = {"metric": f"prefill and decode tok/s, {names[0]} beside {' and '.join(names[1:])} at equal sizes", "unit": "tokens/s",
            "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic: random weights, random token ids",
            "peaks": pk, "prefill_tokens": T, "decode_batch": B, "decode_context": ctx0, "steps": K, "warmup": W,
@@ -337,7 +363,7 @@ def main():
                     help="layer sizes: the benchmark's (default) or another shape BASELINE.json names")
     ap.add_argument("--prompt-max", type=int, default=0, help="longest prompt drawn (default: the shape's own)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
-    ap.add_argument("--design", default=None, choices=["salepel", "zufadra", "dumalix"],
+    ap.add_argument("--design", default=None, choices=["salepel", "zufadra", "dumalix", "fugavik"],
                     help="instead of the default workload: this design beside the closest existing model at equal "
                          "sizes (prefill of --prefill-tokens, decode at --batch; sizes from --sizes)")
     ap.add_argument("--sizes", default="s,m", help="with --design: which of the named sizes (s, m)")

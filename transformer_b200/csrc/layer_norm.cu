@@ -9,8 +9,10 @@
 //
 //   N(a; w, b, eps, center) = (a - m) / sqrt(mean((a - m)^2) + eps) * w + b,   m = center ? mean(a) : 0,  b may be null
 //
-// The variance is the mean of the squared deviations from the mean that was taken first (two passes over the row,
-// which lives in shared memory as floats between them).  One block per row.
+// The variance is the mean of the squared deviations from the mean: every thread takes the mean and the squared
+// deviations of its own entries in two passes, and the threads' statistics are joined exactly (one reduction over
+// the block instead of two).  The row lives in shared memory as floats between the passes.  One block per row;
+// 16-byte accesses where the width and the addresses allow them.
 #include "common.cuh"
 
 struct LayerNormArgs {
@@ -33,93 +35,166 @@ struct LayerNormArgs {
     int d;
 };
 
-// mean (or zero) and 1 / sqrt(var + eps) of the row in shared memory
+// Two partial statistics (count, mean, sum of squared deviations from that mean) joined into one: exact however
+// the entries were dealt out, and as accurate as taking the mean first and the deviations in a second pass.
+struct LnStat {
+    float n, mean, m2;
+};
+__device__ __forceinline__ LnStat ln_join(const LnStat& a, const LnStat& b) {
+    LnStat r;
+    r.n = a.n + b.n;
+    if (r.n == 0.f) {
+        r.mean = r.m2 = 0.f;
+        return r;
+    }
+    const float dm = b.mean - a.mean, fb = b.n / r.n;
+    r.mean = a.mean + dm * fb;
+    r.m2 = a.m2 + b.m2 + dm * dm * a.n * fb;
+    return r;
+}
+__device__ __forceinline__ LnStat ln_block_join(LnStat v, float* red) {      // red: 3 * 32 + 3 floats
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        LnStat w{__shfl_xor_sync(0xffffffffu, v.n, o), __shfl_xor_sync(0xffffffffu, v.mean, o),
+                 __shfl_xor_sync(0xffffffffu, v.m2, o)};
+        v = ln_join(v, w);
+    }
+    __syncthreads();
+    if (lane == 0) {
+        red[3 * warp] = v.n;
+        red[3 * warp + 1] = v.mean;
+        red[3 * warp + 2] = v.m2;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        LnStat t{0.f, 0.f, 0.f};
+        if (lane < nw) t = LnStat{red[3 * lane], red[3 * lane + 1], red[3 * lane + 2]};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            LnStat w{__shfl_xor_sync(0xffffffffu, t.n, o), __shfl_xor_sync(0xffffffffu, t.mean, o),
+                     __shfl_xor_sync(0xffffffffu, t.m2, o)};
+            t = ln_join(t, w);
+        }
+        if (lane == 0) {
+            red[96] = t.n;
+            red[97] = t.mean;
+            red[98] = t.m2;
+        }
+    }
+    __syncthreads();
+    return LnStat{red[96], red[97], red[98]};
+}
+
+// mean (or zero) and 1 / sqrt(var + eps) of the row in shared memory; every thread takes the entries it wrote itself
+template <int W>
 __device__ __forceinline__ void ln_stats(const float* row, int d, bool center, float eps, float* red, float& mean,
                                          float& rstd) {
-    mean = 0.f;
-    if (center) {
-        float s = 0.f;
-        for (int c = threadIdx.x; c < d; c += blockDim.x) s += row[c];
-        mean = block_sum(s, red) / (float)d;
+    float s = 0.f, cnt = 0.f;
+    for (int c = threadIdx.x * W; c < d; c += blockDim.x * W) {
+#pragma unroll
+        for (int e = 0; e < W; ++e) s += center ? row[c + e] : row[c + e] * row[c + e];
+        cnt += (float)W;
     }
-    float ss = 0.f;
-    for (int c = threadIdx.x; c < d; c += blockDim.x) {
-        const float a = row[c] - mean;
-        ss += a * a;
+    if (!center) {
+        mean = 0.f;
+        rstd = 1.0f / sqrtf(block_sum(s, red) / (float)d + eps);
+        return;
     }
-    rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
+    LnStat mine{cnt, cnt > 0.f ? s / cnt : 0.f, 0.f};
+    for (int c = threadIdx.x * W; c < d; c += blockDim.x * W) {
+#pragma unroll
+        for (int e = 0; e < W; ++e) {
+            const float a = row[c + e] - mine.mean;
+            mine.m2 += a * a;
+        }
+    }
+    const LnStat all = ln_block_join(mine, red);
+    mean = all.mean;
+    rstd = 1.0f / sqrtf(all.m2 / (float)d + eps);
+}
+
+// W consecutive entries as floats, one 16-byte access per 8 bfloat16 or 4 floats where VEC says the layout allows it
+template <typename T, bool VEC> __device__ __forceinline__ void ln_load(const T* p, float (&f)[VEC ? 8 : 1]) {
+    if constexpr (VEC) load8(p, f);
+    else f[0] = ldf(p);
+}
+template <typename T, bool VEC> __device__ __forceinline__ void ln_store(T* p, const float (&f)[VEC ? 8 : 1]) {
+    if constexpr (VEC) store8(p, f);
+    else stf(p, f[0]);
 }
 
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) post_add_layernorm_kernel(const LayerNormArgs a) {
     pdl_sync();
     extern __shared__ __align__(16) float ln_row[];     // [d]
-    __shared__ float red[33];
+    __shared__ float red[99];
     const int i = blockIdx.x, d = a.d;
     const int r = a.rows ? a.rows[i] : i;
     float* xr = a.x + (size_t)r * d;
     const T* dr = a.delta ? static_cast<const T*>(a.delta) + (size_t)r * d : nullptr;
     const T* wy = static_cast<const T*>(a.wy);
     const bool has_u = dr != nullptr || wy != nullptr;
-    constexpr int W = VEC ? 4 : 1;
+    constexpr int W = VEC ? 8 : 1;
     if (has_u) {
         for (int c = threadIdx.x * W; c < d; c += blockDim.x * W) {
             float u[W];
-#pragma unroll
-            for (int e = 0; e < W; ++e) u[e] = 0.f;
             if (dr) {
-#pragma unroll
-                for (int e = 0; e < W; ++e) u[e] = ldf(dr + c + e);
+                ln_load<T, VEC>(dr + c, u);
             } else {
+#pragma unroll
+                for (int e = 0; e < W; ++e) u[e] = 0.f;
                 for (int j = 0; j < a.k; ++j) {
                     const float wj = a.topk_w ? a.topk_w[(size_t)r * a.k + j] : 1.f;
-                    const T* src = wy + (size_t)a.pair_row[(size_t)r * a.k + j] * d + c;
+                    float t[W];
+                    ln_load<T, VEC>(wy + (size_t)a.pair_row[(size_t)r * a.k + j] * d + c, t);
 #pragma unroll
-                    for (int e = 0; e < W; ++e) u[e] += wj * ldf(src + e);
+                    for (int e = 0; e < W; ++e) u[e] += wj * t[e];
                 }
             }
 #pragma unroll
             for (int e = 0; e < W; ++e) ln_row[c + e] = u[e];
         }
         float mean = 0.f, rstd = 1.f;
-        if (a.post_w) {
-            __syncthreads();
-            ln_stats(ln_row, d, a.post_center != 0, a.post_eps, red, mean, rstd);
-        }
+        if (a.post_w) ln_stats<W>(ln_row, d, a.post_center != 0, a.post_eps, red, mean, rstd);
         // each thread goes on with the entries it wrote itself
         for (int c = threadIdx.x * W; c < d; c += blockDim.x * W) {
+            float xv[W], pw[W], pb[W];
+            ln_load<float, VEC>(xr + c, xv);
+            if (a.post_w) ln_load<float, VEC>(a.post_w + c, pw);
+            if (a.post_b) ln_load<float, VEC>(a.post_b + c, pb);
 #pragma unroll
             for (int e = 0; e < W; ++e) {
                 float u = ln_row[c + e];
-                if (a.post_w) u = (u - mean) * rstd * a.post_w[c + e] + (a.post_b ? a.post_b[c + e] : 0.f);
-                const float v = xr[c + e] + u;
-                if (!a.rows) xr[c + e] = v;
-                ln_row[c + e] = v;
+                if (a.post_w) u = (u - mean) * rstd * pw[e] + (a.post_b ? pb[e] : 0.f);
+                xv[e] += u;
+                ln_row[c + e] = xv[e];
             }
+            if (!a.rows) ln_store<float, VEC>(xr + c, xv);
         }
     } else {
         if (!a.y) return;
         for (int c = threadIdx.x * W; c < d; c += blockDim.x * W) {
+            float xv[W];
+            ln_load<float, VEC>(xr + c, xv);
 #pragma unroll
-            for (int e = 0; e < W; ++e) ln_row[c + e] = xr[c + e];
+            for (int e = 0; e < W; ++e) ln_row[c + e] = xv[e];
         }
     }
     if (!a.y) return;
     T* yr = static_cast<T*>(a.y) + (size_t)i * d;
-    if (!a.w) {
-        for (int c = threadIdx.x * W; c < d; c += blockDim.x * W) {
-#pragma unroll
-            for (int e = 0; e < W; ++e) stf(yr + c + e, ln_row[c + e]);
-        }
-        return;
-    }
-    __syncthreads();
-    float mean, rstd;
-    ln_stats(ln_row, d, a.center != 0, a.eps, red, mean, rstd);
+    float mean = 0.f, rstd = 1.f;
+    if (a.w) ln_stats<W>(ln_row, d, a.center != 0, a.eps, red, mean, rstd);
     for (int c = threadIdx.x * W; c < d; c += blockDim.x * W) {
+        float o[W], w[W], b[W];
+        if (a.w) ln_load<float, VEC>(a.w + c, w);
+        if (a.b) ln_load<float, VEC>(a.b + c, b);
 #pragma unroll
-        for (int e = 0; e < W; ++e)
-            stf(yr + c + e, (ln_row[c + e] - mean) * rstd * a.w[c + e] + (a.b ? a.b[c + e] : 0.f));
+        for (int e = 0; e < W; ++e) {
+            o[e] = ln_row[c + e];       // without weights: the sum itself, rounded once
+            if (a.w) o[e] = (o[e] - mean) * rstd * w[e] + (a.b ? b[e] : 0.f);
+        }
+        ln_store<T, VEC>(yr + c, o);
     }
 }
 
@@ -141,7 +216,9 @@ static int post_add_layernorm_launch(const LayerNormArgs& a, int n_out, cudaStre
                                            160 * 1024));
         raised = true;
     }
-    if (a.d % 4 == 0)
+    const uintptr_t all = (uintptr_t)a.x | (uintptr_t)a.delta | (uintptr_t)a.wy | (uintptr_t)a.post_w |
+                          (uintptr_t)a.post_b | (uintptr_t)a.w | (uintptr_t)a.b | (uintptr_t)a.y;
+    if (a.d % 8 == 0 && (all & 15) == 0)
         TB_LAUNCH((post_add_layernorm_kernel<T, true>), n_out, 256, smem, s, a);
     else
         TB_LAUNCH((post_add_layernorm_kernel<T, false>), n_out, 256, smem, s, a);
