@@ -259,7 +259,7 @@ def test_layer_norm_kernel_in_all_its_forms(dtype):
         y = y * w
         return y if b is None else y + b
 
-    for d in (48, 50, 192, 4096, 13000):
+    for d in (48, 50, 192, 4096, 6008, 13000):
         g = torch.Generator().manual_seed(d)
         n = 6
         x0 = torch.randn(n, d, generator=g) * 2 + 0.5

@@ -11,8 +11,8 @@
 //
 // The variance is the mean of the squared deviations from the mean: every thread takes the mean and the squared
 // deviations of its own entries in two passes, and the threads' statistics are joined exactly (one reduction over
-// the block instead of two).  The row lives in shared memory as floats between the passes.  One block per row;
-// 16-byte accesses where the width and the addresses allow them.
+// the block instead of two).  One block per row.  Widths that are multiples of eight up to 8192 with 16-byte aligned
+// addresses keep the row in registers and move 16 bytes at a time; any other width keeps it in shared memory as floats.
 #include "common.cuh"
 
 struct LayerNormArgs {
@@ -198,6 +198,119 @@ __global__ void __launch_bounds__(256) post_add_layernorm_kernel(const LayerNorm
     }
 }
 
+// The same with the row in registers: NCH pieces of eight entries a thread (widths that are multiples of eight up to
+// 2048 * NCH, 16-byte aligned addresses).  Nothing goes through shared memory but the reductions.
+template <int NCH>
+__device__ __forceinline__ void ln_stats_reg(const float (&v)[NCH][8], int d, bool center, float eps, float* red,
+                                             float& mean, float& rstd) {
+    float s = 0.f, cnt = 0.f;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+        if ((int)(threadIdx.x + j * 256) * 8 < d) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s += center ? v[j][e] : v[j][e] * v[j][e];
+            cnt += 8.f;
+        }
+    }
+    if (!center) {
+        mean = 0.f;
+        rstd = 1.0f / sqrtf(block_sum(s, red) / (float)d + eps);
+        return;
+    }
+    LnStat mine{cnt, cnt > 0.f ? s / cnt : 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+        if ((int)(threadIdx.x + j * 256) * 8 < d) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float a = v[j][e] - mine.mean;
+                mine.m2 += a * a;
+            }
+        }
+    }
+    const LnStat all = ln_block_join(mine, red);
+    mean = all.mean;
+    rstd = 1.0f / sqrtf(all.m2 / (float)d + eps);
+}
+
+template <typename T, int NCH>
+__global__ void __launch_bounds__(256) post_add_layernorm_reg_kernel(const LayerNormArgs a) {
+    pdl_sync();
+    __shared__ float red[99];
+    const int i = blockIdx.x, d = a.d;
+    const int r = a.rows ? a.rows[i] : i;
+    float* xr = a.x + (size_t)r * d;
+    const T* dr = a.delta ? static_cast<const T*>(a.delta) + (size_t)r * d : nullptr;
+    const T* wy = static_cast<const T*>(a.wy);
+    const bool has_u = dr != nullptr || wy != nullptr;
+    float v[NCH][8];
+    if (has_u) {
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) {
+            const int c = (threadIdx.x + j * 256) * 8;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[j][e] = 0.f;
+            if (c >= d) continue;
+            if (dr) {
+                load8(dr + c, v[j]);
+            } else {
+                for (int q = 0; q < a.k; ++q) {
+                    const float wq = a.topk_w ? a.topk_w[(size_t)r * a.k + q] : 1.f;
+                    float t[8];
+                    load8(wy + (size_t)a.pair_row[(size_t)r * a.k + q] * d + c, t);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[j][e] += wq * t[e];
+                }
+            }
+        }
+        float mean = 0.f, rstd = 1.f;
+        if (a.post_w) ln_stats_reg<NCH>(v, d, a.post_center != 0, a.post_eps, red, mean, rstd);
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) {
+            const int c = (threadIdx.x + j * 256) * 8;
+            if (c >= d) continue;
+            float xv[8], pw[8], pb[8];
+            load8(xr + c, xv);
+            if (a.post_w) load8(a.post_w + c, pw);
+            if (a.post_b) load8(a.post_b + c, pb);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float u = v[j][e];
+                if (a.post_w) u = (u - mean) * rstd * pw[e] + (a.post_b ? pb[e] : 0.f);
+                v[j][e] = xv[e] + u;
+            }
+            if (!a.rows) store8(xr + c, v[j]);
+        }
+    } else {
+        if (!a.y) return;
+#pragma unroll
+        for (int j = 0; j < NCH; ++j) {
+            const int c = (threadIdx.x + j * 256) * 8;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[j][e] = 0.f;
+            if (c < d) load8(xr + c, v[j]);
+        }
+    }
+    if (!a.y) return;
+    T* yr = static_cast<T*>(a.y) + (size_t)i * d;
+    float mean = 0.f, rstd = 1.f;
+    if (a.w) ln_stats_reg<NCH>(v, d, a.center != 0, a.eps, red, mean, rstd);
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+        const int c = (threadIdx.x + j * 256) * 8;
+        if (c >= d) continue;
+        float o[8], w[8], b[8];
+        if (a.w) load8(a.w + c, w);
+        if (a.b) load8(a.b + c, b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            o[e] = v[j][e];             // without weights: the sum itself, rounded once
+            if (a.w) o[e] = (o[e] - mean) * rstd * w[e] + (a.b ? b[e] : 0.f);
+        }
+        store8(yr + c, o);
+    }
+}
+
 template <typename T>
 static int post_add_layernorm_launch(const LayerNormArgs& a, int n_out, cudaStream_t s) {
     if (n_out < 0 || a.d <= 0 || !a.x) return TB_ERR_ARG;
@@ -208,6 +321,15 @@ static int post_add_layernorm_launch(const LayerNormArgs& a, int n_out, cudaStre
     const size_t smem = (size_t)a.d * sizeof(float);
     if (smem > 160 * 1024) return TB_ERR_UNSUPPORTED;
     if (n_out == 0) return 0;
+    const uintptr_t all = (uintptr_t)a.x | (uintptr_t)a.delta | (uintptr_t)a.wy | (uintptr_t)a.post_w |
+                          (uintptr_t)a.post_b | (uintptr_t)a.w | (uintptr_t)a.b | (uintptr_t)a.y;
+    const bool vec = a.d % 8 == 0 && (all & 15) == 0;
+    if (vec && a.d <= 8192) {       // the row in registers
+        if (a.d <= 2048) TB_LAUNCH((post_add_layernorm_reg_kernel<T, 1>), n_out, 256, 0, s, a);
+        else if (a.d <= 4096) TB_LAUNCH((post_add_layernorm_reg_kernel<T, 2>), n_out, 256, 0, s, a);
+        else TB_LAUNCH((post_add_layernorm_reg_kernel<T, 4>), n_out, 256, 0, s, a);
+        return tb_last_error();
+    }
     static bool raised = false;
     if (smem > 48 * 1024 && !raised) {
         tb_note_error(cudaFuncSetAttribute(post_add_layernorm_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -216,9 +338,7 @@ static int post_add_layernorm_launch(const LayerNormArgs& a, int n_out, cudaStre
                                            160 * 1024));
         raised = true;
     }
-    const uintptr_t all = (uintptr_t)a.x | (uintptr_t)a.delta | (uintptr_t)a.wy | (uintptr_t)a.post_w |
-                          (uintptr_t)a.post_b | (uintptr_t)a.w | (uintptr_t)a.b | (uintptr_t)a.y;
-    if (a.d % 8 == 0 && (all & 15) == 0)
+    if (vec)
         TB_LAUNCH((post_add_layernorm_kernel<T, true>), n_out, 256, smem, s, a);
     else
         TB_LAUNCH((post_add_layernorm_kernel<T, false>), n_out, 256, smem, s, a);
