@@ -76,6 +76,21 @@ def test_tensor_plan_names_every_tensor_of_a_model_file(name):
     assert all(v is not None for v in chosen.values())
 
 
+def test_random_model_folder_has_the_design_s_tensor_names(tmp_path):
+    import random
+    import transformer_b200 as tb
+    from transformer_b200.weights.loader import check_rules, open_tensors
+    for cfg in (T.MIXED, T.random_config(random.Random(5), True), T.random_config(random.Random(6), False)):
+        folder = tb.write_random_model(str(tmp_path / f"m{cfg['width']}_{cfg['vocab']}"), cfg, seed=1)
+        arch, meta = _typed(cfg)
+        files = open_tensors(folder)
+        present = {n: files.shape_dtype(n) for n in files.names()}
+        check_rules(arch.tensor_plan(meta), present, folder)
+        read, tensors = FP.read_folder(folder)
+        assert _typed(read)[1] == meta
+        assert FP.forward(read, tensors, [1, 2, 3]).shape == (3, cfg["vocab"])
+
+
 def test_plain_layer_norm_and_sink_softmax():
     g = torch.Generator().manual_seed(0)
     x = torch.randn(4, 10, generator=g, dtype=torch.float64) * 3 + 1

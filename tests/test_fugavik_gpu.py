@@ -211,6 +211,38 @@ def test_sizes_that_no_fast_kernel_takes(dtype, folders):
         assert float((lg[i] - rows[n - 1]).abs().max()) <= tol, f"request {i} in a batch"
 
 
+@pytest.mark.parametrize("seed", [0, 1, 2, 3, 4, 5])
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """Layers of every kind in an order drawn at random, sizes drawn at random (two of three draws take sizes that
+    reach the vector and tensor-core forms): a prompt across several pages and twelve decoded tokens."""
+    import random
+    rng = random.Random(1000 + seed)
+    cfg = T.random_config(rng, nice=seed % 3 != 2)
+    folder = T.make_folder(tmp_path, f"drawn{seed}", cfg=cfg, seed=seed)
+    cfg, tensors = FP.read_folder(folder)
+    n = rng.randrange(150, 330)
+    tokens = random_prompts(cfg["vocab"], [n + 12], seed)[0]
+    for dtype in DTYPES:
+        rows, routes = T.run_cuts(_load(folder, dtype), tokens, [n])
+        kinds = " ".join(l["type"][0] + (l["mlp"]["kind"][0] if l["mlp"] else "-") for l in cfg["layers"])
+        T.check_request(cfg, tensors, tokens, rows, dtype, f"drawn {seed} ({kinds}, width {cfg['width']})", routes,
+                        floor=True)
+
+
+def test_random_weights_on_the_device_equal_the_written_folder(tmp_path):
+    """``tb.random_model`` (weights filled on the device) and ``tb.write_random_model`` + ``tb.load`` give the same
+    model: the same logits bit for bit."""
+    import transformer_b200 as tb
+    cfg = T.CONFIGS["mixed"][0]
+    folder = tb.write_random_model(str(tmp_path / "written"), cfg, seed=5, std=0.1)
+    tokens = random_prompts(cfg["vocab"], [70], 1)[0]
+    a = tb.load(folder, dtype="bfloat16", max_tokens=512)
+    b = tb.random_model(cfg, seed=5, dtype="bfloat16", max_tokens=512, std=0.1)
+    la = a.step([a.open()], [tokens], [list(range(70))]).cpu()
+    lb = b.step([b.open()], [tokens], [list(range(70))]).cpu()
+    assert torch.equal(la, lb)
+
+
 def test_greedy_generation_through_the_entry_point(folders):
     import transformer_b200 as tb
     cfg, tensors = FP.read_folder(folders["mixed"])

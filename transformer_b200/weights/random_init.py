@@ -30,7 +30,7 @@ def _host_piece(name: str, shape, init: str, seed: int, std: float) -> torch.Ten
         n = 1
         for s in shape:
             n *= int(s)
-        return torch.from_numpy(counter_random.normal_values(seed, name, 0, n, std)).view(*shape)
+        return torch.from_numpy(counter_random.normal_values(seed, name, 0, n, std)).reshape(tuple(shape))
     raise ValueError(f"unknown init {init!r}")
 
 
