@@ -91,6 +91,23 @@ def test_random_model_folder_has_the_design_s_tensor_names(tmp_path):
         assert FP.forward(read, tensors, [1, 2, 3]).shape == (3, cfg["vocab"])
 
 
+def test_a_blending_number_that_nothing_reads_may_be_there_or_not():
+    """The first blending layer does not use its number, a layer that does not blend has none: a file may carry
+    either all the same; only a later blending layer's number is asked for."""
+    from transformer_b200.weights.loader import WeightError, check_rules
+    cfg, seed = T.CONFIGS["mixed"]
+    arch, meta = _typed(cfg)
+    rules = arch.tensor_plan(meta)
+    tensors = T.random_tensors(cfg, seed)
+    present = {n: (tuple(t.shape), "BF16") for n, t in tensors.items()}
+    assert "l2.mix.vmix" in present and "l0.mix.vmix" not in present      # layer 2 is the source, layer 0 does not blend
+    check_rules(rules, present, "as written")
+    check_rules(rules, dict(present, **{"l0.mix.vmix": ((), "BF16")}), "one more")
+    check_rules(rules, {n: v for n, v in present.items() if n != "l2.mix.vmix"}, "one fewer")
+    with pytest.raises(WeightError):
+        check_rules(rules, {n: v for n, v in present.items() if n != "l4.mix.vmix"}, "a blender without its number")
+
+
 def test_plain_layer_norm_and_sink_softmax():
     g = torch.Generator().manual_seed(0)
     x = torch.randn(4, 10, generator=g, dtype=torch.float64) * 3 + 1

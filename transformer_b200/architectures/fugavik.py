@@ -80,6 +80,7 @@ def build_spec(m: FugavikMeta) -> ModelSpec:
 
 def tensor_plan(m: FugavikMeta) -> List[TensorRule]:
     d = m.width
+    source = m.first_v_mix()
     rules = [TensorRule(("embedding", "table"), (m.vocab, d), "matrix", (single("embed", (m.vocab, d)),))]
     for i, layer in enumerate(m.layers):
         p, L = f"l{i}.", ("layers", i)
@@ -106,8 +107,10 @@ def tensor_plan(m: FugavikMeta) -> List[TensorRule]:
             vec(mx + ("q_norm",), "mix.q.norm", x.dim, "ones")
             vec(mx + ("k_norm",), "mix.k.norm", x.dim, "ones")
             vec(mx + ("sink",), "mix.sink", x.heads)
-            if x.v_mix:
+            if x.v_mix and i != source:
                 vec(mx + ("vmix",), "mix.vmix", None)
+            else:       # the first blending layer's number is not used; a layer that does not blend has no use for one
+                rules.append(TensorRule(mx + ("vmix",), (), "norm", (single(p + "mix.vmix", ()),), unused=True))
             mat(mx + ("wo",), "mix.o", (d, ho))
         elif isinstance(x, LatentMeta):
             hq, r = x.heads * x.dim, x.kv_rank

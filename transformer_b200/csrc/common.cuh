@@ -122,6 +122,9 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
 
 // ---- gated activations of a feed-forward's (gate, up) pair ------------------------------------------
 // kind 0: silu(g) * u.   kind 1: g' = min(g, limit), u' = clamp(u, -limit, limit);  g' * sigmoid(alpha g') * (u' + 1).
+// kind 2 stands beside them for a feed-forward WITHOUT a gate: a product of one matrix whose result passes
+// max(z, 0)^2 in the epilogue (TB_ACT_RELU2; the kernels apply it where they do not have a pair).
+#define TB_ACT_RELU2 2
 struct GluRule {
     int kind;
     float alpha, limit;

@@ -132,7 +132,12 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const GemmArgs a) {
             const int n = n0 + tx * 4 + j;
             if (n >= a.N) continue;
             float v = acc[i][j];
-            if (DUAL) v = glu_apply(v, acc2[i][j], a.glu);
+            if (DUAL) {
+                v = glu_apply(v, acc2[i][j], a.glu);
+            } else if (a.glu.kind == TB_ACT_RELU2) {
+                v = fmaxf(v, 0.f);
+                v *= v;
+            }
             stf(C + (size_t)m * a.ldc + n, v);
         }
     }
@@ -191,7 +196,8 @@ batched_rows_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restr
 
 
 extern "C" {
-// out_kind: 0 = C has the type of A and B, 1 = C is float, 2 = swiglu pair (C has the type of A)
+// out_kind: 0 = C has the type of A and B, 1 = C is float, 2 = swiglu pair (C has the type of A),
+// 3 = max(., 0)^2 of the product (C has the type of A)
 #define TB_GEMM(NAME, T)                                                                                        \
     int NAME(const void* A, const int* a_rows, const void* B, void* C, const int* group_offsets,               \
              long long b_group_stride, int lda, int ldb, int ldc, int M, int N, int K, int G, int out_kind,    \
@@ -201,6 +207,10 @@ extern "C" {
         if (out_kind == 0) return gemm_simt_launch<T, T, false>(a, s);                                          \
         if (out_kind == 1) return gemm_simt_launch<T, float, false>(a, s);                                      \
         if (out_kind == 2) return gemm_simt_launch<T, T, true>(a, s);                                           \
+        if (out_kind == 3) {                                                                                    \
+            a.glu.kind = TB_ACT_RELU2;                                                                          \
+            return gemm_simt_launch<T, T, false>(a, s);                                                         \
+        }                                                                                                       \
         return TB_ERR_ARG;                                                                                      \
     }
 TB_GEMM(tb_gemm_simt_f32, float)

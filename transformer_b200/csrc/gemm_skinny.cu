@@ -242,7 +242,12 @@ __global__ void __launch_bounds__(WK * WN * 32) gemm_skinny_kernel(const SkinnyA
                 v += red[w_n][w][0][r][c];
                 if (DUAL) v2 += red[w_n][w][NMAT - 1][r][c];
             }
-            if (DUAL) v = glu_apply(v, v2, a.glu);
+            if (DUAL) {
+                v = glu_apply(v, v2, a.glu);
+            } else if (a.glu.kind == TB_ACT_RELU2) {
+                v = fmaxf(v, 0.f);
+                v *= v;
+            }
             stf(static_cast<TY*>(a.Y) + (size_t)(listed ? list[chunk + r] : chunk + r) * a.ldy + nb0 + cc, v);
         }
     }
@@ -278,10 +283,12 @@ static int skinny_launch_nt(const SkinnyArgs& a, int out_kind, cudaStream_t s) {
     if (out_kind == 0) return skinny_launch_shape<NT, false, __nv_bfloat16>(a, s);
     if (out_kind == 1) return skinny_launch_shape<NT, false, float>(a, s);
     if (out_kind == 2) return skinny_launch_shape<NT, true, __nv_bfloat16>(a, s);
+    if (out_kind == 3) return skinny_launch_shape<NT, false, __nv_bfloat16>(a, s);     // a.glu.kind says relu2
     return TB_ERR_ARG;
 }
 
-// out_kind: 0 = bfloat16 out, 1 = float out, 2 = swiglu pair (bfloat16 out).  M is the number of rows
+// out_kind: 0 = bfloat16 out, 1 = float out, 2 = swiglu pair (bfloat16 out), 3 = max(., 0)^2 of the product
+// (bfloat16 out).  M is the number of rows
 // over all groups; max_group_rows bounds the rows of any ONE group (for experts: the number of tokens,
 // since a token picks an expert at most once) and only chooses how many rows a pass takes at once.
 // w_constant: W holds weights, which no kernel writes, so a block may read its first weights before it waits for
@@ -317,7 +324,8 @@ int tb_gemm_skinny_bf16(const void* X, const int* x_rows, const void* W, void* Y
                         long long w_group_stride, int ldx, int ldw, int ldy, int M, int N, int K, int G, int out_kind,
                         int max_group_rows, const int* row_group, int x_div, int w_constant, cudaStream_t s) {
     return skinny_entry(X, x_rows, W, Y, group_offsets, w_group_stride, ldx, ldw, ldy, M, N, K, G, out_kind,
-                        max_group_rows, row_group, x_div, w_constant, GluRule{0, 0.f, 0.f}, s);
+                        max_group_rows, row_group, x_div, w_constant,
+                        GluRule{out_kind == 3 ? TB_ACT_RELU2 : 0, 0.f, 0.f}, s);
 }
 // The (gate, up) pair product with the clamped form of the gate (see GluRule, kind 1).
 int tb_gemm_skinny_glu_bf16(const void* X, const int* x_rows, const void* W, void* Y, const int* group_offsets,

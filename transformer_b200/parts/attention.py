@@ -150,7 +150,7 @@ class Attention(Mixer):
             decl["temp"] = ParamDecl((self.nh,), "norm", "ones")
         if self.sink:
             decl["sink"] = ParamDecl((self.nh,), "norm", "normal")
-        if self.value_mix:      # the source has the number too and does not use it
+        if self.value_mix == "blend":
             decl["vmix"] = ParamDecl((), "norm", "normal")
         if self.position is not None:      # what the position encoding has learned travels with its mixer
             decl.update({"position." + n: d for n, d in self.position.parameters().items()})

@@ -73,7 +73,9 @@ class DenseSwiGLU(FeedForward):
 @FEED_FORWARDS.register("mlp")
 class DenseMLP(FeedForward):
     """params: width, di, act ("relu2").  A feed-forward without a gate: out = act(x1 Wu^T) Wd^T, with
-    relu2(z) = max(z, 0)^2 (float, one rounding) applied to the first product's result in place."""
+    relu2(z) = max(z, 0)^2 (float, one rounding).  The activation sits in the epilogue of this package's own products
+    (decoding, and the 32-bit path); behind the library's product of many bfloat16 rows it is a pass of its own over
+    the result, in place."""
     graph_safe = True
     launches_only = True
 
@@ -91,8 +93,11 @@ class DenseMLP(FeedForward):
     def forward(self, ctx, x1, out) -> None:
         nt = x1.shape[0]
         h = ctx.scratch("ff.h", (nt, self.di), self.dtype)
-        matmul_nt(x1, self.weights["wu"], h)
-        lib.call("tb_relu2_" + lib.suffix(self.dtype), lib.ptr(h), nt * self.di)
+        if self.dtype == torch.float32:
+            linear.gemm_simt(x1, self.weights["wu"], h, out_kind=3)
+        elif not (nt <= linear.SKINNY_MAX_ROWS and gemm_skinny(x1, self.weights["wu"], h, out_kind=3)):
+            matmul_nt(x1, self.weights["wu"], h)
+            lib.call("tb_relu2_" + lib.suffix(self.dtype), lib.ptr(h), nt * self.di)
         matmul_nt(h, self.weights["wd"], out)
 
 

@@ -89,6 +89,9 @@ def check_rules(rules: Sequence[TensorRule], present: Mapping[str, Tuple[Tuple[i
     wrong_shape = []
     wrong_type = []
     for rule in rules:
+        if rule.unused:
+            used.update(n for src in rule.sources for n in src.names if n in present)
+            continue
         pick = None
         for src in rule.sources:
             if all(n in present for n in src.names):
@@ -144,6 +147,7 @@ def load_weights(path: str, rules: Sequence[TensorRule], compute_dtype: torch.dt
     present = {n: files.shape_dtype(n) for n in files.names()}
     chosen = check_rules(rules, present, path)
     out: Dict[Dest, torch.Tensor] = {}
+    rules = [r for r in rules if not r.unused]
     for rule in rules:
         src = chosen[rule.dest]
         if src is None:

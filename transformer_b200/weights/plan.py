@@ -52,6 +52,8 @@ class TensorRule:
     sources: Tuple[Source, ...]
     init: str = "normal"                    # how the random-weights mode fills it: "normal" | "ones"
     shared_with: Optional[Dest] = None      # when no source is present, reuse this parameter (tied head)
+    unused: bool = False                    # a tensor that a file may carry and no part reads: taken note of when it
+                                            # is there (so that it is not reported as unexpected), never asked for
 
     @property
     def canonical(self) -> Source:

@@ -40,8 +40,8 @@ def random_file_tensors(rules: Sequence[TensorRule], seed: int, matrix_dtype: to
     (a parameter may be joined from several file tensors: each is drawn under its own name)."""
     out: Dict[str, torch.Tensor] = {}
     for rule in rules:
-        if rule.shared_with is not None:
-            continue   # tied: the file holds no tensor of its own
+        if rule.shared_with is not None or rule.unused:
+            continue   # tied: the file holds no tensor of its own; unused: nothing would read it
         for name, shape in zip(rule.canonical.names, rule.canonical.shapes):
             t = _host_piece(name, shape, rule.init, int(seed), std)
             out[name] = t.to(storage_dtype(rule.role, matrix_dtype)).contiguous()
@@ -66,7 +66,7 @@ def random_device_weights(rules: Sequence[TensorRule], seed: int, compute_dtype:
     out: Dict[Dest, torch.Tensor] = {}
     with torch.cuda.device(device):
         for rule in rules:
-            if rule.shared_with is not None:
+            if rule.shared_with is not None or rule.unused:
                 continue
             dtype = storage_dtype(rule.role, compute_dtype)
             if rule.init == "ones":
@@ -85,6 +85,6 @@ def random_device_weights(rules: Sequence[TensorRule], seed: int, compute_dtype:
                 raise ValueError(f"{rule.dest}: the canonical file tensors do not join to the parameter's shape")
             out[rule.dest] = t
     for rule in rules:
-        if rule.shared_with is not None:
+        if rule.shared_with is not None and not rule.unused:
             out[rule.dest] = out[rule.shared_with]
     return out
