@@ -531,3 +531,57 @@ def test_rows_scaled_for_experts_that_weight_what_they_read(dtype):
                 want = (w.view(-1)[p] * x[p // k].float()).to(td)
                 at = int(pair_row[p]) if rows is not None else p
                 assert torch.equal(out[at].cpu(), want), f"pair {p}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rule", [0, 2])
+def test_layer_norm_kernel_with_a_router_riding_along(dtype, rule):
+    """The router of the rows the kernel has just written, as stored: the same experts and weights as the router's own
+    kernel gives for those rows, and as torch gives (rule 0: softmax over the kept logits; rule 2: sigmoids)."""
+    from transformer_b200.csrc import lib
+    td = torch.float32 if dtype == "float32" else torch.bfloat16
+    sfx = "f32" if dtype == "float32" else "bf16"
+    for d, E, k in ((48, 5, 2), (192, 8, 1), (2048, 16, 4), (4096, 3, 3)):
+        g = torch.Generator().manual_seed(d + rule)
+        n = 7
+        x0 = torch.randn(n, d, generator=g)
+        delta = (torch.randn(n, d, generator=g) * 2).to(td)
+        pw, pb = torch.rand(d, generator=g) + 0.5, torch.randn(d, generator=g) * 0.3
+        wr = (torch.randn(E, d, generator=g) * (3.0 / d ** 0.5)).to(td)
+        x, y = x0.clone().cuda(), torch.empty(n, d, dtype=td, device="cuda")
+        idx = torch.full((n, k), -1, dtype=torch.int32, device="cuda")
+        wts = torch.zeros(n, k, device="cuda")
+        d_delta, d_pw, d_pb, d_wr = delta.cuda(), pw.cuda(), pb.cuda(), wr.cuda()
+        lib.call("tb_post_add_layernorm_router_" + sfx, lib.ptr(x), lib.ptr(d_delta), 0, 0, 0, 0, lib.ptr(d_pw),
+                 lib.ptr(d_pb), 1e-5, 1, 0, 0, 0, 0.0, 0, lib.ptr(y), n, d, lib.ptr(d_wr), 0, lib.ptr(idx), lib.ptr(wts),
+                 E, k, rule)
+        x2, y2 = x0.clone().cuda(), torch.empty(n, d, dtype=td, device="cuda")
+        lib.call("tb_post_add_layernorm_" + sfx, lib.ptr(x2), lib.ptr(d_delta), 0, 0, 0, 0, lib.ptr(d_pw), lib.ptr(d_pb),
+                 1e-5, 1, 0, 0, 0, 0.0, 0, lib.ptr(y2), n, d)
+        torch.cuda.synchronize()
+        assert torch.equal(y, y2) and torch.equal(x, x2)
+        z = y.cpu().double() @ wr.double().T
+        top = torch.topk(z, k, dim=-1)
+        assert torch.equal(idx.cpu().long(), top.indices), f"width {d}"
+        want = torch.sigmoid(top.values) if rule == 2 else torch.softmax(top.values, dim=-1)
+        assert float((wts.cpu().double() - want).abs().max()) < 1e-5, f"width {d}"
+
+
+def test_squared_relu_in_the_products_epilogue():
+    from transformer_b200.parts.linear import gemm_simt, gemm_skinny
+    g = torch.Generator().manual_seed(0)
+    for M, K, N in ((3, 64, 40), (8, 2048, 96), (16, 128, 24)):
+        a = torch.randn(M, K, generator=g)
+        w = torch.randn(N, K, generator=g) / K ** 0.5
+        want = torch.relu(a.double() @ w.double().T) ** 2
+        out = torch.empty(M, N, device="cuda")
+        d_a, d_w = a.cuda(), w.cuda()
+        gemm_simt(d_a, d_w, out, out_kind=3)
+        assert float((out.cpu().double() - want).abs().max()) < 1e-5 * max(1.0, float(want.abs().max()))
+        ab, wb = a.bfloat16(), w.bfloat16()
+        want = torch.relu(ab.double() @ wb.double().T) ** 2
+        out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        d_a, d_w = ab.cuda(), wb.cuda()
+        assert gemm_skinny(d_a, d_w, out, out_kind=3)
+        torch.cuda.synchronize()
+        assert float((out.cpu().double() - want).abs().max()) <= 2.0 ** -7 * float(want.abs().max())

@@ -13,7 +13,19 @@
 // deviations of its own entries in two passes, and the threads' statistics are joined exactly (one reduction over
 // the block instead of two).  One block per row.  Widths that are multiples of eight up to 8192 with 16-byte aligned
 // addresses keep the row in registers and move 16 bytes at a time; any other width keeps it in shared memory as floats.
+//
+// A router may ride along (the form with the row in registers, up to 256 rows): the logits of the row just written,
+// as stored, against the router's matrix, a warp per output, and the choice by the rules of router_pick.cuh.
 #include "common.cuh"
+#include "router_pick.cuh"
+
+struct LayerNormTail {
+    const void* w;          // [E, d] router matrix in the activations' type, or null: none
+    const float* bias;      // the scored rule's correction, or null
+    int* idx;               // [rows, k]
+    float* wts;             // [rows, k]
+    int E, k, rule;         // rule: RouterRule::scored
+};
 
 struct LayerNormArgs {
     float* x;
@@ -33,6 +45,7 @@ struct LayerNormArgs {
     int center;
     void* y;
     int d;
+    LayerNormTail tail;
 };
 
 // Two partial statistics (count, mean, sum of squared deviations from that mean) joined into one: exact however
@@ -233,9 +246,10 @@ __device__ __forceinline__ void ln_stats_reg(const float (&v)[NCH][8], int d, bo
     rstd = 1.0f / sqrtf(all.m2 / (float)d + eps);
 }
 
-template <typename T, int NCH>
+template <typename T, int NCH, bool TAIL>
 __global__ void __launch_bounds__(256) post_add_layernorm_reg_kernel(const LayerNormArgs a) {
     pdl_sync();
+    extern __shared__ __align__(16) unsigned char ln_tail_smem[];      // TAIL: the row as T [d], then logits [E] (or 2 E)
     __shared__ float red[99];
     const int i = blockIdx.x, d = a.d;
     const int r = a.rows ? a.rows[i] : i;
@@ -308,6 +322,34 @@ __global__ void __launch_bounds__(256) post_add_layernorm_reg_kernel(const Layer
             if (a.w) o[e] = (o[e] - mean) * rstd * w[e] + (a.b ? b[e] : 0.f);
         }
         store8(yr + c, o);
+        if (TAIL) store8(reinterpret_cast<T*>(ln_tail_smem) + c, o);      // what the router reads: the row as stored
+    }
+    if (!TAIL) return;
+    __syncthreads();
+    constexpr int EPL = Vec16<T>::N;
+    const T* ys = reinterpret_cast<const T*>(ln_tail_smem);
+    float* lg = reinterpret_cast<float*>(ln_tail_smem + (size_t)d * sizeof(T));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const LayerNormTail& t = a.tail;
+    for (int e = warp; e < t.E; e += 8) {
+        const T* we = static_cast<const T*>(t.w) + (size_t)e * d;
+        float acc = 0.f;
+        for (int c = lane * EPL; c < d; c += 32 * EPL) {
+            float xf[EPL], wf[EPL];
+            Vec16<T>::load(ys + c, xf);
+            Vec16<T>::load(we + c, wf);
+#pragma unroll
+            for (int q = 0; q < EPL; ++q) acc += xf[q] * wf[q];
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) lg[e] = acc;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        if (t.rule == 1)
+            router_pick_scored(lg, lg + t.E, t.bias, t.idx + (size_t)i * t.k, t.wts + (size_t)i * t.k, t.E, t.k, lane);
+        else
+            router_pick(lg, t.idx + (size_t)i * t.k, t.wts + (size_t)i * t.k, t.E, t.k, lane, t.rule == 2);
     }
 }
 
@@ -324,10 +366,21 @@ static int post_add_layernorm_launch(const LayerNormArgs& a, int n_out, cudaStre
     const uintptr_t all = (uintptr_t)a.x | (uintptr_t)a.delta | (uintptr_t)a.wy | (uintptr_t)a.post_w |
                           (uintptr_t)a.post_b | (uintptr_t)a.w | (uintptr_t)a.b | (uintptr_t)a.y;
     const bool vec = a.d % 8 == 0 && (all & 15) == 0;
+    if (a.tail.w) {
+        // the form that also routes: a few rows, the row in registers, the row as stored and the logits in 40 KB
+        const LayerNormTail& t = a.tail;
+        if (t.E <= 0 || t.k <= 0 || t.k > t.E || !t.idx || !t.wts || !a.y) return TB_ERR_ARG;
+        const size_t tsm = (size_t)a.d * sizeof(T) + (size_t)t.E * sizeof(float) * (t.rule == 1 ? 2 : 1);
+        if (!vec || a.d > 8192 || n_out > 256 || tsm > 40 * 1024 || ((uintptr_t)t.w & 15)) return TB_ERR_UNSUPPORTED;
+        if (a.d <= 2048) TB_LAUNCH((post_add_layernorm_reg_kernel<T, 1, true>), n_out, 256, tsm, s, a);
+        else if (a.d <= 4096) TB_LAUNCH((post_add_layernorm_reg_kernel<T, 2, true>), n_out, 256, tsm, s, a);
+        else TB_LAUNCH((post_add_layernorm_reg_kernel<T, 4, true>), n_out, 256, tsm, s, a);
+        return tb_last_error();
+    }
     if (vec && a.d <= 8192) {       // the row in registers
-        if (a.d <= 2048) TB_LAUNCH((post_add_layernorm_reg_kernel<T, 1>), n_out, 256, 0, s, a);
-        else if (a.d <= 4096) TB_LAUNCH((post_add_layernorm_reg_kernel<T, 2>), n_out, 256, 0, s, a);
-        else TB_LAUNCH((post_add_layernorm_reg_kernel<T, 4>), n_out, 256, 0, s, a);
+        if (a.d <= 2048) TB_LAUNCH((post_add_layernorm_reg_kernel<T, 1, false>), n_out, 256, 0, s, a);
+        else if (a.d <= 4096) TB_LAUNCH((post_add_layernorm_reg_kernel<T, 2, false>), n_out, 256, 0, s, a);
+        else TB_LAUNCH((post_add_layernorm_reg_kernel<T, 4, false>), n_out, 256, 0, s, a);
         return tb_last_error();
     }
     static bool raised = false;
@@ -353,7 +406,21 @@ extern "C" {
                                     const float* b, float eps, int center, void* y, int n_out, int d,                 \
                                     cudaStream_t s) {                                                                 \
         LayerNormArgs a{x, delta, wy, pair_row, topk_w, k, post_w, post_b, post_eps, post_center, rows, w, b, eps,    \
-                        center, y, d};                                                                                \
+                        center, y, d, LayerNormTail{nullptr, nullptr, nullptr, nullptr, 0, 0, 0}};                    \
+        return post_add_layernorm_launch<T>(a, n_out, s);                                                             \
+    }                                                                                                                 \
+    /* The same with a router riding along: router_w [E, d]; rule 0: the route_k largest logits with a softmax over   \
+       the kept, 1: softmax over all and score + bias, 2: sigmoids as they are.  TB_ERR_UNSUPPORTED (nothing done)    \
+       for more than 256 rows, widths or addresses the register form does not take. */                               \
+    int tb_post_add_layernorm_router_##SFX(float* x, const void* delta, const void* wy, const int* pair_row,          \
+                                           const float* topk_w, int k, const float* post_w, const float* post_b,      \
+                                           float post_eps, int post_center, const int* rows, const float* w,          \
+                                           const float* b, float eps, int center, void* y, int n_out, int d,          \
+                                           const void* router_w, const float* route_bias, int* route_idx,             \
+                                           float* route_w, int E, int route_k, int rule, cudaStream_t s) {            \
+        if (!router_w || rule < 0 || rule > 2) return TB_ERR_ARG;                                                     \
+        LayerNormArgs a{x, delta, wy, pair_row, topk_w, k, post_w, post_b, post_eps, post_center, rows, w, b, eps,    \
+                        center, y, d, LayerNormTail{router_w, route_bias, route_idx, route_w, E, route_k, rule}};     \
         return post_add_layernorm_launch<T>(a, n_out, s);                                                             \
     }
 TB_LAYERNORM(f32, float)
@@ -363,3 +430,5 @@ TB_LAYERNORM(bf16, __nv_bfloat16)
 #include "tape.h"
 TB_TAPE_REGISTER(tb_post_add_layernorm_f32)
 TB_TAPE_REGISTER(tb_post_add_layernorm_bf16)
+TB_TAPE_REGISTER(tb_post_add_layernorm_router_f32)
+TB_TAPE_REGISTER(tb_post_add_layernorm_router_bf16)

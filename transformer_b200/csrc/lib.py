@@ -78,6 +78,8 @@ _SIGNATURES: Dict[str, str] = {
     "tb_moe_scaled_rows_f32": "ppppiii", "tb_moe_scaled_rows_bf16": "ppppiii",
     "tb_relu2_f32": "pl", "tb_relu2_bf16": "pl",
     "tb_post_add_layernorm_f32": "pppppippfipppfipii", "tb_post_add_layernorm_bf16": "pppppippfipppfipii",
+    "tb_post_add_layernorm_router_f32": "pppppippfipppfipiippppiii",
+    "tb_post_add_layernorm_router_bf16": "pppppippfipppfipiippppiii",
 }
 class TapeArg(ctypes.Union):
     _fields_ = [("p", ctypes.c_void_p), ("i", ctypes.c_int), ("f", ctypes.c_float), ("l", ctypes.c_longlong),

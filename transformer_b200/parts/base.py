@@ -154,6 +154,12 @@ class NormTail:
     scores: Any = None
     scored: bool = False     # "router": softmax over all outputs, choice by score + bias, weights = the chosen scores
     bias: Any = None
+    sigmoid: bool = False    # "router": the k largest logits, weights = their sigmoids as they are
+
+    @property
+    def rule(self) -> int:
+        """The kernels' number of the rule of choice (csrc/router_pick.cuh)."""
+        return 2 if self.sigmoid else 1 if self.scored else 0
 
 
 class Norm(Part):

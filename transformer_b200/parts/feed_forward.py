@@ -219,12 +219,13 @@ class MoE(FeedForward):
 
     def norm_tail(self, ctx, nt):
         """For a few tokens the router rides along with the norm before this part."""
-        if nt > ROUTER_TAIL_ROWS or self.scoring == "sigmoid":
+        if nt > ROUTER_TAIL_ROWS:
             return None
         return NormTail("router", weights=self.weights["router"], k=self.k,
                         index=ctx.scratch("moe.topk_idx", (nt, self.k), torch.int32),
                         scores=ctx.scratch("moe.topk_w", (nt, self.k), torch.float32),
-                        scored=self.scoring == "all", bias=self.weights.get("correction"))
+                        scored=self.scoring == "all", bias=self.weights.get("correction"),
+                        sigmoid=self.scoring == "sigmoid")
 
     def forward(self, ctx, x1, out, tail=None) -> None:
         nt = x1.shape[0]

@@ -39,6 +39,11 @@ class RMSNorm(Norm):
             self.weights["weight"] = self.weights["weight"].float() * self.mult
 
     def forward(self, ctx, x, delta, rows, y, warm=None, tail=None) -> None:
+        if tail is not None and tail.sigmoid and not (isinstance(delta, NormedDelta) and delta.center):
+            # this norm's own kernels know the two other rules of choice: the router runs behind it
+            self.forward(ctx, x, delta, rows, y, warm=warm)
+            _route(lib.suffix(self.dtype), y, tail, y.shape[0], self.width)
+            return
         if isinstance(delta, NormedDelta):
             post_add_rmsnorm(self.dtype, x, delta, rows, self.weights["weight"], self.eps, y, tail=tail)
             return
@@ -140,14 +145,21 @@ class NoNorm(Norm):
     takes_weighted_rows = True
     takes_normed_delta = True
     takes_pair_delta = True
+    tails = ("router",)
 
     def __init__(self, params, dtype, device):
         super().__init__(params, dtype, device)
         self.width = int(params["width"])
 
-    def forward(self, ctx, x, delta, rows, y) -> None:
+    def forward(self, ctx, x, delta, rows, y, tail=None) -> None:
+        """``tail``: the router of the part that reads y; it rides in the kernel that norms a layer-normed delta, and
+        runs behind any other."""
         if isinstance(delta, NormedDelta):
-            post_add_rmsnorm(self.dtype, x, delta, rows, None, 0.0, y)
+            post_add_rmsnorm(self.dtype, x, delta, rows, None, 0.0, y, tail=tail)
+            return
+        if tail is not None:
+            self.forward(ctx, x, delta, rows, y)
+            _route(lib.suffix(self.dtype), y, tail, y.shape[0], self.width)
             return
         if isinstance(delta, PairDelta):
             pair_add_rmsnorm(self.dtype, x, delta, rows, None, y, None, None, 0.0)
@@ -163,7 +175,10 @@ class NoNorm(Norm):
 def _route(sfx, y, tail, n_out, width) -> None:
     """The router of the rows ``y`` by a kernel of its own, into the tail's index and scores."""
     E = tail.weights.shape[0]
-    if tail.scored:
+    if tail.sigmoid:
+        lib.call("tb_router_sigmoid_" + sfx, lib.ptr(y), lib.ptr(tail.weights), lib.ptr(tail.index), lib.ptr(tail.scores),
+                 0, 0, 0, 0, n_out, width, E, tail.k)
+    elif tail.scored:
         lib.call("tb_router_scored_" + sfx, lib.ptr(y), lib.ptr(tail.weights), lib.ptr(tail.bias), lib.ptr(tail.index),
                  lib.ptr(tail.scores), 0, 0, 0, 0, n_out, width, E, tail.k)
     else:
@@ -175,16 +190,14 @@ def post_add_rmsnorm(dtype, x, pending: NormedDelta, rows, weight, eps, y, tail=
     """x[rows] += pending.delta / rms(pending.delta) * pending.weight (written back when ``rows`` is None), then
     y = x / rms(x) * weight; with ``y`` None only the sum.  ``tail``: a "router" NormTail computed along the way."""
     if pending.center or pending.bias is not None:
-        post_add_layernorm(dtype, x, pending.delta, pending, rows, weight, None, eps, False, y)
-        if tail is not None:
-            _route(lib.suffix(dtype), y, tail, y.shape[0], x.shape[1])
+        post_add_layernorm(dtype, x, pending.delta, pending, rows, weight, None, eps, False, y, tail=tail)
         return
     delta, wy, idx, wts, k = pending.delta, None, None, None, 0
     if isinstance(delta, WeightedRows):
         wy, idx, wts, k, delta = delta.rows, delta.index, delta.weights, delta.k, None
     n_out = x.shape[0] if y is None else y.shape[0]
     sfx = lib.suffix(dtype)
-    if tail is not None and rows is None and y is not None:
+    if tail is not None and rows is None and y is not None and weight is not None and not tail.sigmoid:
         if lib.try_call("tb_post_add_rmsnorm_router_" + sfx, lib.ptr(x), lib.ptr(delta), lib.ptr(wy), lib.ptr(idx),
                         lib.ptr(wts), k, lib.ptr(pending.weight), float(pending.eps), lib.ptr(weight), float(eps),
                         lib.ptr(y), lib.ptr(tail.weights), lib.ptr(tail.bias), lib.ptr(tail.index), lib.ptr(tail.scores),
@@ -197,10 +210,11 @@ def post_add_rmsnorm(dtype, x, pending: NormedDelta, rows, weight, eps, y, tail=
         _route(sfx, y, tail, n_out, x.shape[1])
 
 
-def post_add_layernorm(dtype, x, delta, post, rows, weight, bias, eps, center, y) -> None:
+def post_add_layernorm(dtype, x, delta, post, rows, weight, bias, eps, center, y, tail=None) -> None:
     """x[rows] += N_post(delta) (written back when ``rows`` is None), then y = N(x[rows]; weight, bias, eps, center).
     ``delta``: a tensor, a :class:`WeightedRows` or None; ``post``: the :class:`NormedDelta` whose norm the delta
-    still has to pass (None: it joins as it is); ``weight`` None: y is the sum itself; ``y`` None: only the sum."""
+    still has to pass (None: it joins as it is); ``weight`` None: y is the sum itself; ``y`` None: only the sum.
+    ``tail``: a "router" NormTail of the rows y, in the same kernel where its form takes the sizes, else behind it."""
     wy = idx = wts = None
     k = 0
     if isinstance(delta, WeightedRows):
@@ -210,9 +224,18 @@ def post_add_layernorm(dtype, x, delta, post, rows, weight, bias, eps, center, y
     pe, pc = 0.0, 0
     if post is not None:
         pw, pb, pe, pc = post.weight, post.bias, float(post.eps), 1 if post.center else 0
+    if tail is not None and y is not None:
+        if lib.try_call("tb_post_add_layernorm_router_" + lib.suffix(dtype), lib.ptr(x), lib.ptr(delta), lib.ptr(wy),
+                        lib.ptr(idx), lib.ptr(wts), k, lib.ptr(pw), lib.ptr(pb), pe, pc, lib.ptr(rows), lib.ptr(weight),
+                        lib.ptr(bias), float(eps), 1 if center else 0, lib.ptr(y), n_out, x.shape[1],
+                        lib.ptr(tail.weights), lib.ptr(tail.bias), lib.ptr(tail.index), lib.ptr(tail.scores),
+                        tail.weights.shape[0], tail.k, tail.rule):
+            return
     lib.call("tb_post_add_layernorm_" + lib.suffix(dtype), lib.ptr(x), lib.ptr(delta), lib.ptr(wy), lib.ptr(idx),
              lib.ptr(wts), k, lib.ptr(pw), lib.ptr(pb), pe, pc, lib.ptr(rows), lib.ptr(weight), lib.ptr(bias), float(eps),
              1 if center else 0, lib.ptr(y), n_out, x.shape[1])
+    if tail is not None and y is not None:
+        _route(lib.suffix(dtype), y, tail, n_out, x.shape[1])
 
 
 def pair_add_rmsnorm(dtype, x, pending, rows, w1, y1, w2, y2, eps) -> None:
